@@ -1,0 +1,109 @@
+"""CPU: the C oracle against the golden fixtures made from the reference's own Python."""
+import hashlib
+
+import numpy as np
+import pytest
+
+import oracle
+
+P = oracle.P
+
+
+def test_field_vectors(golden):
+    g = golden.field_vectors
+    for a, b, s, d, m, pw, iv in zip(g["a"], g["b"], g["add"], g["sub"], g["mul"], g["pow12345"], g["inv"]):
+        a, b = int(a), int(b)
+        assert oracle.gl_add(a, b) == int(s)
+        assert oracle.gl_sub(a, b) == int(d)
+        assert oracle.gl_mul(a, b) == int(m)
+        assert oracle.gl_pow(a, 12345) == int(pw)
+        if a:
+            assert oracle.gl_inv(a) == int(iv)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8, 16, 64, 256, 1024, 4096])
+def test_ntt_vectors(golden, n):
+    g = golden.ntt_vectors
+    x = g[f"in_{n}"]
+    assert np.array_equal(oracle.ntt(x), g[f"fwd_{n}"])
+    assert np.array_equal(oracle.ntt(x, invert=True), g[f"inv_{n}"])
+    rows = np.stack([x, g[f"fwd_{n}"]])
+    assert np.array_equal(oracle.ntt_batched(rows)[0], g[f"fwd_{n}"])
+    assert np.array_equal(oracle.ntt_batched(rows, invert=True)[1], x)
+
+
+@pytest.mark.parametrize("tag", ["8_8_32", "16_32_128", "64_64_256", "48_64_256"])
+def test_encode_and_commit_vectors(golden, tag):
+    g = golden.encode_vectors
+    ell, k, n = (int(v) for v in tag.split("_"))
+    msg = g[f"msg_{tag}"]
+    padded = np.zeros((msg.shape[0], k), dtype=np.uint64)
+    padded[:, :ell] = msg
+    polys, codes = oracle.encode_rows(padded, n)
+    assert np.array_equal(codes, g[f"code_{tag}"])
+    assert np.array_equal(oracle.ntt_batched(polys), padded)
+    leaves = oracle.hash_columns(codes)
+    assert np.array_equal(leaves, g[f"leaves_{tag}"])
+    levels = oracle.merkle_levels(leaves)
+    assert levels[-1].tobytes() == g[f"root_{tag}"].tobytes()
+    assert b"".join(l.tobytes() for l in levels) == g[f"tree_{tag}"].tobytes()
+    assert oracle.commit_rows(padded, n) == g[f"root_{tag}"].tobytes()
+
+
+def test_config1(golden):
+    import random
+    g = golden.config1
+    r = random.Random(0)
+    msg = np.array([[r.randrange(P) for _ in range(1024)] for _ in range(64)], dtype=np.uint64)
+    _, codes = oracle.encode_rows(msg, 4096, want_polys=False)
+    assert hashlib.sha256(codes.tobytes()).digest() == g["code_sha256"].tobytes()
+    assert np.array_equal(codes[g["rows_idx"]], g["rows"])
+    assert np.array_equal(codes[:, g["cols_idx"]], g["cols"])
+    leaves = oracle.hash_columns(codes)
+    assert hashlib.sha256(leaves.tobytes()).digest() == g["leaves_sha256"].tobytes()
+    assert np.array_equal(leaves[:8], g["leaves_head"])
+    assert oracle.merkle_levels(leaves)[-1].tobytes() == g["root"].tobytes()
+
+
+def test_blake3_and_column_trees(golden):
+    g = golden.hash_vectors
+    for n, d in zip(g["b3_lengths"], g["b3_digests"]):
+        assert oracle.blake3(bytes(i % 251 for i in range(int(n)))) == d.tobytes()
+    for key in g.files:
+        if not key.startswith("mat_"):
+            continue
+        tag = key[4:]
+        leaves = oracle.hash_columns(g[key])
+        assert np.array_equal(leaves, g[f"leaves_{tag}"]), tag
+        assert b"".join(l.tobytes() for l in oracle.merkle_levels(leaves)) == g[f"tree_{tag}"].tobytes(), tag
+
+
+def test_prf_prg_coins(golden):
+    g = golden.hash_vectors
+    seed = g["chal_seed"].tobytes()
+    for label in ("", "lin", "irs", "quad"):
+        want = g[f"chal_{label or 'none'}"]
+        got = [oracle.challenge(seed, int(c), label.encode()) for c in g["chal_cids"]]
+        assert got == [int(v) for v in want]
+    assert np.array_equal(oracle.row_prg_indexed(seed, g["prg_rows"], 9), g["prg"])
+    assert np.array_equal(oracle.row_prg(seed, 0, 3, 9), g["prg"][:3])
+
+
+@pytest.mark.parametrize("qt", ["Q4_K", "Q5_K", "Q6_K"])
+def test_kquant_vectors(golden, qt):
+    g = golden.kquant_vectors
+    got = oracle.kquant_to_field(g[f"raw_{qt}"], qt, float(g["S"][0]))
+    assert np.array_equal(got, g[f"field_{qt}"])
+
+
+@pytest.mark.parametrize("name", ["deg3_n6", "deg2_n4", "terms_n6", "mixed_n8", "single_n1"])
+def test_sumcheck_vectors(golden, name):
+    g = golden.sumcheck_vectors
+    terms = []
+    for row in g[f"{name}_terms"]:
+        vals = [int(v) for v in row]
+        terms.append((vals[0], [v for v in vals[1:] if v >= 0]))
+    claim, samples, _ = oracle.sumcheck(g[f"{name}_tables"], terms, [int(c) for c in g[f"{name}_coins"]])
+    assert claim == int(g[f"{name}_claim"][0])
+    want = g[f"{name}_polys"]
+    assert np.array_equal(samples[:, :want.shape[1]], want)
