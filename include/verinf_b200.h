@@ -1,0 +1,188 @@
+/*
+ * verinf_b200 — C ABI of the B200 (sm_100a) kernels for VerInf's prover
+ * field-arithmetic hot path.
+ *
+ * Conventions
+ *  - Every pointer named *_dev or typed as data (uint64_t*, uint8_t*) is a DEVICE
+ *    pointer into memory the caller owns; the library allocates no outputs.
+ *  - Field elements are uint64_t in canonical form [0, p), p = 2^64 - 2^32 + 1.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *  - Every function returns 0 on success; non-zero means nothing useful was
+ *    written and vi_last_error() holds a message.  The library never exits the
+ *    process and never traps the device.
+ *  - The only memory the library owns are immutable per-device twiddle tables,
+ *    allocated (cudaMalloc + synchronous upload) the first time a transform
+ *    length is used on a device.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative to
+ * the reference project root).  A ctypes binding of these symbols is what the
+ * drop-in modules verinf_b200/cuda_primitives.py and kquant_cuda.py use.
+ */
+#ifndef VERINF_B200_H
+#define VERINF_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Text of the last error raised on the calling thread. */
+const char* vi_last_error(void);
+
+/* ---- elementwise field ops ------------------------------------------------
+ * replace gl_mul/gl_add/gl_sub/gl_neg/gl_pow/gl_inv_batched/gl_axpy_inplace
+ * (prover/cuda_primitives.py:208-303, prover/kernels/gl_extras.cuh:22-40).
+ * op: 0 = mul, 1 = add, 2 = sub.  out may alias a or b. */
+int vi_gl_binary(int op, const uint64_t* a, const uint64_t* b, uint64_t* out, int64_t n, void* stream);
+/* out[i] = a[i] op b[i % nb]: the broadcast form callers build today with
+ * .expand().contiguous() (prover/core.py:738-739, layergkr/gpu.py:189). */
+int vi_gl_binary_bcast(int op, const uint64_t* a, const uint64_t* b, int64_t nb, uint64_t* out, int64_t n, void* stream);
+int vi_gl_neg(const uint64_t* a, uint64_t* out, int64_t n, void* stream);
+int vi_gl_pow(const uint64_t* base, uint64_t exp, uint64_t* out, int64_t n, void* stream);
+int vi_gl_axpy(uint64_t* y, uint64_t alpha, const uint64_t* x, int64_t n, void* stream);
+
+/* ---- NTT --------------------------------------------------------------------
+ * replaces ntt_forward/ntt_inverse(_batched) (prover/cuda_primitives.py:347-409,
+ * prover/kernels/ntt.cuh:310-770).  In place over m contiguous rows of length n
+ * (power of two, 2 <= n <= 2^20), natural order in and out; the inverse scales by
+ * n^-1.  Transforms longer than 1024 need scratch (any size >= n*8 bytes works;
+ * vi_ntt_scratch_bytes gives the size that keeps a row chunk L2-resident). */
+int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n);
+int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
+                   void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ---- Reed-Solomon row encode ---------------------------------------------------
+ * replaces encode_messages + _coset_encode_codewords (prover/core.py:721-802) and
+ * layergkr's encode_batch_ntt (layergkr/gpu.py:141-203): message row = values of a
+ * degree-<K polynomial at the K-th roots of unity (slots [ell,K) are the pad);
+ * polys[r] = its coefficients; codes[r][j] = its value at 7*w_N^j.
+ *   msg      (m, ell) row-major
+ *   pad_mode 0: pad slots are zero (layergkr); 1: pad slot k of row r is
+ *            u64le(BLAKE3(seed || (row_off+r)_le8 || k_le8)[0:8]) % p  (row_prg)
+ *   seed_dev 32 bytes on the device (pad_mode 1)
+ *   polys    (m, K) or NULL;  codes (m, N) or NULL
+ *   scratch  >= (K + N)*8 bytes (K*8 when codes is NULL); see vi_encode_scratch_bytes */
+int64_t vi_encode_scratch_bytes(int64_t m, int64_t k, int64_t n);
+int vi_encode_rows(const uint64_t* msg, int64_t m, int64_t ell, int64_t k, int64_t n,
+                   int pad_mode, const uint8_t* seed_dev, int64_t row_off,
+                   uint64_t* polys, uint64_t* codes,
+                   void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ---- ZK pad PRG ---------------------------------------------------------------
+ * replaces row_prg / row_prg_indexed (prover/cuda_primitives.py:877-974).
+ * out (n_rows, slack).  rows_dev == NULL means rows row_off .. row_off+n_rows-1. */
+int vi_row_prg(const uint8_t* seed_dev, int64_t row_off, const uint64_t* rows_dev,
+               int64_t n_rows, int64_t slack, uint64_t* out, void* stream);
+
+/* ---- challenge PRF --------------------------------------------------------------
+ * replaces challenge_vec / challenge_at (prover/cuda_primitives.py:549-591,
+ * prover/kernels/gl_spmv.cuh:51-66): out[i] = int(BLAKE3(seed || label ||
+ * cid_le8)[:16], LE) % p with cid = cids_dev ? cids_dev[i] : i.  label_len <= 8. */
+int vi_challenge(const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
+                 const uint64_t* cids_dev, int64_t n, uint64_t* out, void* stream);
+
+/* ---- BLAKE3 column hash ---------------------------------------------------------
+ * replaces hash_columns_streamed (prover/cuda_primitives.py:796-808,
+ * prover/kernels/blake3_columns.cuh:47-174): digest j = BLAKE3-256 of the bytes
+ * le8(mat[0,j]) || le8(mat[1,j]) || ... of column j of the row-major (m, ncols)
+ * matrix.  digests (ncols, 32).  scratch holds per-segment subtree chaining values;
+ * vi_hash_columns_scratch_bytes gives the size (0 when a single segment is used). */
+int64_t vi_hash_columns_scratch_bytes(int64_t m, int64_t ncols);
+int vi_hash_columns(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* digests,
+                    void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Streaming form: replaces hash_columns_stream_init/update/finalize and the state
+ * machine behind MerkleColumnAccumulator (prover/cuda_primitives.py:813-853,976-987,
+ * 1297-1385; prover/kernels/blake3_columns.cuh:184-328).  The state is a caller-owned
+ * buffer of vi_hash_stream_state_bytes(ncols, total_rows) bytes; no initialisation
+ * is needed.  Feed the rows in order: every call but the last must bring a multiple
+ * of 128 rows; rows_done is the number of rows fed before this call.  The call that
+ * reaches total_rows writes the digests. */
+int64_t vi_hash_stream_state_bytes(int64_t ncols, int64_t total_rows);
+int vi_hash_stream_update(void* state, int64_t ncols, int64_t total_rows, int64_t rows_done,
+                          const uint64_t* rows, int64_t n_rows, uint8_t* digests, void* stream);
+
+/* ---- Merkle tree ----------------------------------------------------------------
+ * replaces merkle_build_blake3 / merkle_one_level (prover/cuda_primitives.py:990-1004,
+ * 1388-1401; prover/kernels/merkle.cuh:18-37): parent = BLAKE3-256(left || right) as a
+ * 64-byte message; an odd level pairs its last node with itself.
+ * upper receives levels 1.. (level i has ceil(n_{i-1}/2) nodes) back to back:
+ * vi_merkle_upper_nodes(n) nodes of 32 bytes; the root is the last one. */
+int64_t vi_merkle_upper_nodes(int64_t n_leaves);
+int vi_merkle_build(const uint8_t* leaves, int64_t n_leaves, uint8_t* upper, void* stream);
+int vi_merkle_level(const uint8_t* nodes, int64_t n_nodes, uint8_t* parents, void* stream);
+
+/* ---- K-quant lift -----------------------------------------------------------------
+ * replaces kquant_to_field (prover/kquant_cuda.py:60-177): raw GGUF super-blocks ->
+ * field integers round_half_even(double(v) * S), negative values as p - |v|, in stored
+ * order.  qtype 4 = Q4_K (144 B), 5 = Q5_K (176 B), 6 = Q6_K (210 B); out n_blocks*256. */
+int vi_kquant_to_field(const uint8_t* raw, int64_t n_blocks, int qtype, double S,
+                       uint64_t* out, void* stream);
+
+/* Fused lift + encode (no counterpart in the reference; equals kquant_to_field ->
+ * optional transpose as prover/loader.py:433-436 -> row packing of
+ * prover/core.py:389-458 -> encode_messages): the quantised (d_out, d_in) matrix is
+ * lifted inside the encode's first pass, so lifted weights never reach HBM.
+ * Message slot c of row r is flat element f = (first_row + r)*ell + c of the lifted
+ * matrix, transposed (f = k_in*d_out + n_out) when transpose != 0; slots past the end
+ * of the matrix are zero.  Other arguments as vi_encode_rows. */
+int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, int64_t d_out, int64_t d_in,
+                          int transpose, int64_t first_row, int64_t m,
+                          int64_t ell, int64_t k, int64_t n,
+                          int pad_mode, const uint8_t* seed_dev, int64_t row_off,
+                          uint64_t* polys, uint64_t* codes,
+                          void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ---- sumcheck ---------------------------------------------------------------------
+ * replaces the per-round work of prove_terms_gpu / fold_t / gl_sum
+ * (layergkr/gpu.py:326-410; CPU twin layergkr/sumcheck.py:153-226).
+ * A problem is n_tables multilinear tables of `size` entries (power of two; entry i of
+ * table k at tables[k*stride + i]) and n_terms products: term t = coefs[t] *
+ * prod_{j < nfac[t]} table[fac[t*4 + j]]  (at most 8 tables, 8 terms, 4 factors).
+ *   vi_sumcheck_claim   sum over the hypercube of all terms -> out[0]
+ *   vi_sumcheck_round   if fold != 0 first folds every table with challenge r
+ *                       (f'[i] = f[i] + r*(f[half+i] - f[i]), size -> size/2, in place),
+ *                       then writes the round samples g(0..deg) of the (folded) tables
+ *                       to out[0..deg].  `size` is the table length BEFORE the fold.
+ *                       With size/2 == 1 after folding no samples exist; the final
+ *                       values are tables[k*stride].
+ * partials: scratch of vi_sumcheck_scratch_bytes() bytes.  out: device, >= 8 u64. */
+int64_t vi_sumcheck_scratch_bytes(void);
+int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_tables, int64_t size,
+                      int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
+                      uint64_t* out, void* partials, void* stream);
+int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
+                      int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
+                      int fold, uint64_t r, uint64_t* out, void* partials, void* stream);
+
+/* ---- remaining exports of the reference module (not on the hot path) -------------
+ * poly_eval (prover/kernels/gl_extras.cuh:93-108), gl_matmul / gl_matvec
+ * (prover/kernels/gl_matmul.cuh:28-59), gl_spmv / gl_spmv_challenged
+ * (prover/kernels/gl_spmv.cuh:25-90), lookup multiplicities
+ * (prover/kernels/gl_extras.cuh:118-149). */
+int vi_poly_eval(const uint64_t* coeffs, int64_t m, int64_t d, const uint64_t* points, int64_t k,
+                 uint64_t* out, void* stream);
+int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n, void* stream);
+int vi_gl_matvec(const uint64_t* M, const uint64_t* v, uint64_t* w, int64_t m, int64_t n, void* stream);
+int vi_gl_spmv(const uint64_t* values, const uint64_t* col_idx, const uint64_t* row_ptr,
+               const uint64_t* x, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
+               uint64_t* y, int64_t n_rows, void* stream);   /* x == NULL: challenged form */
+int vi_lookup_multiplicities(const uint64_t* x, int64_t n_x, const uint64_t* table, int64_t n_table,
+                             uint64_t* mult, void* stream);   /* table == NULL: range table [0, n_table) */
+
+/* q_lin band interpreters (prover/cuda_primitives.py:605-790).  kind 0 = descriptor
+ * band (u = desc_dev, tblA, tblB, chal_buf), 1 = causal_id (p0=base,p1=m,p2=h,p3=coef),
+ * 2 = causal_c2 (p0=base,p1=h,p2=coef), 3 = embed (p0=base,p1=d,p2=rows_per_w,p3=ell,
+ * aux0 = token ids int64, aux_n = count), 4 = rope_x (p0=base,p1=H,p2=d_h, aux0 = cos,
+ * aux1 = sin). */
+int vi_interp_band(int kind, uint64_t* out, int64_t out_off, int64_t flat_lo, int64_t n_slots,
+                   uint64_t p0, uint64_t p1, uint64_t p2, uint64_t p3,
+                   const uint64_t* desc_dev, const void* aux0, const void* aux1, const uint64_t* chal_buf,
+                   int64_t aux_n, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VERINF_B200_H */

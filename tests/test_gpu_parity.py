@@ -1,0 +1,517 @@
+"""GPU parity: the CUDA path (through the C ABI, via the drop-in modules) against the CPU
+oracle and the golden fixtures.  Integer work: every comparison is bit-exact."""
+import hashlib
+import random
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import oracle  # noqa: E402
+
+P = oracle.P
+
+
+@pytest.fixture(scope="module")
+def cp():
+    from verinf_b200 import cuda_primitives
+    return cuda_primitives
+
+
+def dev(a):
+    a = np.ascontiguousarray(np.asarray(a, dtype=np.uint64))
+    return torch.from_numpy(a.view(np.int64)).cuda().view(torch.uint64)
+
+
+def host(t):
+    return t.contiguous().view(torch.int64).cpu().numpy().view(np.uint64)
+
+
+def rnd_field(rng, shape):
+    """uniform in [0, p) by rejection (p is within 2^-32 of 2^64)"""
+    a = rng.integers(0, 2**64, size=shape, dtype=np.uint64)
+    bad = a >= np.uint64(P)
+    while bad.any():
+        a[bad] = rng.integers(0, 2**64, size=int(bad.sum()), dtype=np.uint64)
+        bad = a >= np.uint64(P)
+    return a
+
+
+# ---------------------------------------------------------------- field ------
+def test_field_golden(cp, golden):
+    g = golden.field_vectors
+    a, b = dev(g["a"]), dev(g["b"])
+    assert np.array_equal(host(cp.gl_add(a, b)), g["add"])
+    assert np.array_equal(host(cp.gl_sub(a, b)), g["sub"])
+    assert np.array_equal(host(cp.gl_mul(a, b)), g["mul"])
+    assert np.array_equal(host(cp.gl_pow(a, 12345)), g["pow12345"])
+    nz = g["a"] != 0
+    assert np.array_equal(host(cp.gl_inv(a))[nz], g["inv"][nz])
+    assert np.array_equal(host(cp.gl_inv_batched(a))[nz], g["inv"][nz])
+    assert np.array_equal(host(cp.gl_neg(a)), np.array([(P - int(x)) % P for x in g["a"]], dtype=np.uint64))
+
+
+def test_field_random_and_axpy(cp):
+    rng = np.random.default_rng(1)
+    n = 100003
+    a, b = rnd_field(rng, n), rnd_field(rng, n)
+    ai, bi = [int(x) for x in a[:2000]], [int(x) for x in b[:2000]]
+    got = host(cp.gl_mul(dev(a), dev(b)))
+    assert [int(x) for x in got[:2000]] == [x * y % P for x, y in zip(ai, bi)]
+    # whole array through linearity: (a*b) + (a*(p-b)) == 0
+    nb = np.where(b == 0, b, np.uint64(P) - b)
+    s = cp.gl_add(cp.gl_mul(dev(a), dev(b)), cp.gl_mul(dev(a), dev(nb)))
+    assert not host(s).any()
+    y, x, alpha = dev(a), dev(b), 0x123456789ABCDEF
+    cp.gl_axpy(y, alpha, x)
+    assert [int(v) for v in host(y)[:2000]] == [(p + alpha * q) % P for p, q in zip(ai, bi)]
+    v = rnd_field(rng, 257)
+    m = rnd_field(rng, (5, 257))
+    got = host(cp.gl_mul_rowvec(dev(m), dev(v)))
+    assert [int(t) for t in got[3]] == [int(p) * int(q) % P for p, q in zip(m[3], v)]
+    assert cp.gl_mul(dev(a[:0]), dev(b[:0])).numel() == 0
+
+
+# ---------------------------------------------------------------- NTT --------
+@pytest.mark.parametrize("n", [2, 4, 8, 16, 64, 256, 1024, 4096])
+def test_ntt_golden(cp, golden, n):
+    g = golden.ntt_vectors
+    x = dev(g[f"in_{n}"])
+    cp.ntt_forward(x)
+    assert np.array_equal(host(x), g[f"fwd_{n}"])
+    cp.ntt_inverse(x)
+    assert np.array_equal(host(x), g[f"in_{n}"])
+    y = dev(g[f"in_{n}"])
+    cp.ntt_inverse(y)
+    assert np.array_equal(host(y), g[f"inv_{n}"])
+
+
+@pytest.mark.parametrize("logn", list(range(1, 15)) + [16, 17, 18])
+@pytest.mark.parametrize("m", [1, 3, 129])
+def test_ntt_batched_vs_oracle(cp, logn, m):
+    if logn >= 16 and m == 129:
+        m = 17
+    rng = np.random.default_rng(100 + logn)
+    n = 1 << logn
+    a = rnd_field(rng, (m, n))
+    x = dev(a)
+    cp.ntt_forward_batched(x)
+    assert np.array_equal(host(x), oracle.ntt_batched(a))
+    cp.ntt_inverse_batched(x)
+    assert np.array_equal(host(x), a)
+    y = dev(a)
+    cp.ntt_inverse_batched(y)
+    assert np.array_equal(host(y), oracle.ntt_batched(a, invert=True))
+
+
+def test_ntt_large_roundtrip_and_errors(cp):
+    rng = np.random.default_rng(7)
+    a = rnd_field(rng, (2, 1 << 20))
+    x = dev(a)
+    cp.ntt_forward_batched(x)
+    assert np.array_equal(host(x)[1], oracle.ntt(a[1]))
+    cp.ntt_inverse_batched(x)
+    assert np.array_equal(host(x), a)
+    with pytest.raises(RuntimeError):
+        cp.ntt_forward(dev(np.arange(12)))
+    with pytest.raises(RuntimeError):
+        cp.ntt_forward(dev(np.arange(16))[::2])
+    with pytest.raises(RuntimeError):
+        cp.ntt_forward(torch.zeros(16, dtype=torch.int64, device="cuda"))
+    e = torch.empty((0, 64), dtype=torch.uint64, device="cuda")
+    cp.ntt_forward_batched(e)
+
+
+def test_poly_ops(cp):
+    rng = np.random.default_rng(9)
+    a, b = rnd_field(rng, 37), rnd_field(rng, 90)
+    want = [0] * (37 + 90 - 1)
+    for i, x in enumerate(a):
+        for j, y in enumerate(b):
+            want[i + j] = (want[i + j] + int(x) * int(y)) % P
+    assert [int(v) for v in host(cp.poly_mul(dev(a), dev(b)))] == want
+    A, B = rnd_field(rng, (3, 40)), rnd_field(rng, (3, 40))
+    got = host(cp.poly_mul_batched(dev(A), dev(B)))
+    assert np.array_equal(got[1], host(cp.poly_mul(dev(A[1]), dev(B[1]))))
+    s = host(cp.poly_add(dev(a), dev(b)))
+    assert [int(v) for v in s[:37]] == [(int(x) + int(y)) % P for x, y in zip(a, b[:37])]
+    pts = rnd_field(rng, 11)
+    ev = host(cp.poly_eval(dev(a), dev(pts)))
+    for p_, e_ in zip(pts, ev):
+        acc = 0
+        for c in reversed(a):
+            acc = (acc * int(p_) + int(c)) % P
+        assert acc == int(e_)
+    assert host(cp.poly_eval(dev(A), dev(pts))).shape == (3, 11)
+
+
+# ---------------------------------------------------------------- encode -----
+@pytest.mark.parametrize("tag", ["8_8_32", "16_32_128", "64_64_256", "48_64_256"])
+def test_encode_golden(cp, golden, tag):
+    g = golden.encode_vectors
+    ell, k, n = (int(v) for v in tag.split("_"))
+    polys, codes = cp.encode_rows(dev(g[f"msg_{tag}"]), k, n)
+    assert np.array_equal(host(codes), g[f"code_{tag}"])
+    back = polys.clone()
+    cp.ntt_forward_batched(back)
+    assert np.array_equal(host(back)[:, :ell], g[f"msg_{tag}"])
+    assert not host(back)[:, ell:].any()
+    leaves = cp.hash_columns_streamed(codes)
+    assert np.array_equal(leaves.cpu().numpy(), g[f"leaves_{tag}"])
+    root, levels = cp.merkle_build_blake3(leaves)
+    assert root.cpu().numpy().tobytes() == g[f"root_{tag}"].tobytes()
+    assert b"".join(l.cpu().numpy().tobytes() for l in levels) == g[f"tree_{tag}"].tobytes()
+    assert levels[0] is leaves and tuple(levels[-1].shape) == (1, 32)
+
+
+def test_config1_golden(cp, golden):
+    g = golden.config1
+    r = random.Random(0)
+    msg = np.array([[r.randrange(P) for _ in range(1024)] for _ in range(64)], dtype=np.uint64)
+    root, levels, codes = cp.commit_rows(dev(msg), 1024, 4096)
+    c = host(codes)
+    assert hashlib.sha256(c.tobytes()).digest() == g["code_sha256"].tobytes()
+    assert np.array_equal(c[g["rows_idx"]], g["rows"])
+    assert np.array_equal(c[:, g["cols_idx"]], g["cols"])
+    assert hashlib.sha256(levels[0].cpu().numpy().tobytes()).digest() == g["leaves_sha256"].tobytes()
+    assert root.cpu().numpy().tobytes() == g["root"].tobytes()
+    assert len(levels) == 13
+
+
+ENC_CASES = [(2, 2, 2, 3), (1, 2, 8, 2), (3, 4, 16, 5), (8, 8, 8, 1), (20, 32, 64, 7), (64, 128, 512, 130),
+             (512, 512, 2048, 9), (1000, 1024, 4096, 4), (2048, 2048, 4096, 3), (8192, 16384, 65536, 5),
+             (30000, 32768, 65536, 2), (65536, 65536, 262144, 3)]
+
+
+@pytest.mark.parametrize("ell,k,n,m", ENC_CASES)
+@pytest.mark.parametrize("pad", [False, True])
+def test_encode_vs_oracle(cp, ell, k, n, m, pad):
+    rng = np.random.default_rng(ell * 7 + k + m)
+    msg = rnd_field(rng, (m, ell))
+    seed = bytes(rng.integers(0, 256, size=32, dtype=np.uint8))
+    row_off = 1000003
+    padded = np.zeros((m, k), dtype=np.uint64)
+    padded[:, :ell] = msg
+    if pad and ell < k:
+        padded[:, ell:] = oracle.row_prg(seed, row_off, m, k - ell)
+    want_p, want_c = oracle.encode_rows(padded, n)
+    seed_t = torch.tensor(list(seed), dtype=torch.uint8, device="cuda") if pad else None
+    polys, codes = cp.encode_rows(dev(msg), k, n, master_seed=seed_t, row_offset=row_off)
+    assert np.array_equal(host(polys), want_p)
+    assert np.array_equal(host(codes), want_c)
+    p2, c2 = cp.encode_rows(dev(msg), k, n, master_seed=seed_t, row_offset=row_off, need_codewords=False)
+    assert c2 is None and np.array_equal(host(p2), want_p)
+    # same as the reference's unfused pipeline on the primitives
+    if pad and ell < k:
+        full = dev(padded)
+        cp.ntt_inverse_batched(full)
+        g = dev(np.array([pow(7, l, P) for l in range(k)], dtype=np.uint64)) if k <= 4096 else None
+        if g is not None:
+            ext = torch.zeros((m, n), dtype=torch.uint64, device="cuda")
+            ext[:, :k] = cp.gl_mul_rowvec(full, g)
+            cp.ntt_forward_batched(ext)
+            assert torch.equal(ext.view(torch.int64), codes.view(torch.int64))
+
+
+def test_encode_edge_cases(cp):
+    e = torch.empty((0, 8), dtype=torch.uint64, device="cuda")
+    p, c = cp.encode_rows(e, 8, 32)
+    assert tuple(p.shape) == (0, 8) and tuple(c.shape) == (0, 32)
+    with pytest.raises(RuntimeError):
+        cp.encode_rows(torch.zeros((2, 9), dtype=torch.uint64, device="cuda"), 8, 32)   # ELL > K
+    with pytest.raises(RuntimeError):
+        cp.encode_rows(torch.zeros((2, 8), dtype=torch.uint64, device="cuda"), 12, 48)  # K not a power of 2
+    rng = np.random.default_rng(3)
+    msgs = rnd_field(rng, (6, 32))
+    out = host(cp.rs_encode_rows(dev(msgs), 128, 32))
+    for i in range(6):
+        co = oracle.ntt(msgs[i], invert=True)
+        ext = np.zeros(128, dtype=np.uint64)
+        ext[:32] = co
+        assert np.array_equal(out[i], oracle.ntt(ext))
+
+
+def test_encode_chunking_invariant(cp):
+    """small scratch (one row per chunk) and large scratch give identical codewords"""
+    from verinf_b200._lib import LIB, check, ptr, stream_ptr
+    rng = np.random.default_rng(17)
+    m, ell, k, n = 11, 3000, 4096, 16384
+    msg = dev(rnd_field(rng, (m, ell)))
+    _, want = cp.encode_rows(msg, k, n, need_polys=False)
+    codes = torch.empty((m, n), dtype=torch.uint64, device="cuda")
+    small = torch.empty(((k + n) * 8,), dtype=torch.uint8, device="cuda")
+    check(LIB.vi_encode_rows(ptr(msg), m, ell, k, n, 0, None, 0, None, ptr(codes), ptr(small), small.numel(),
+                             stream_ptr()))
+    assert torch.equal(codes.view(torch.int64), want.view(torch.int64))
+    rc = LIB.vi_encode_rows(ptr(msg), m, ell, k, n, 0, None, 0, None, ptr(codes), ptr(small), 100, stream_ptr())
+    assert rc != 0 and b"scratch" in LIB.vi_last_error()
+
+
+# ---------------------------------------------------------------- hashing ----
+def test_hash_golden(cp, golden):
+    g = golden.hash_vectors
+    for key in g.files:
+        if not key.startswith("mat_"):
+            continue
+        tag = key[4:]
+        leaves = cp.hash_columns_streamed(dev(g[key]))
+        assert np.array_equal(leaves.cpu().numpy(), g[f"leaves_{tag}"]), tag
+        _, levels = cp.merkle_build_blake3(leaves)
+        assert b"".join(l.cpu().numpy().tobytes() for l in levels) == g[f"tree_{tag}"].tobytes(), tag
+
+
+@pytest.mark.parametrize("m,n", [(1, 1), (5, 33), (128, 100), (129, 100), (255, 7), (256, 64), (257, 64),
+                                 (1000, 300), (4096, 64), (4224, 40), (16385, 9)])
+def test_hash_columns_vs_oracle(cp, m, n):
+    rng = np.random.default_rng(m * 31 + n)
+    a = rnd_field(rng, (m, n))
+    assert np.array_equal(cp.hash_columns_streamed(dev(a)).cpu().numpy(), oracle.hash_columns(a))
+
+
+@pytest.mark.parametrize("total,pieces", [(129, [129]), (129, [1, 128]), (300, [3, 128, 169]),
+                                           (1027, [3, 1024]), (2048, [1024, 1024]), (2051, [3, 1000, 24, 1024]),
+                                           (640, [127, 1, 1, 127, 128, 256])])
+def test_merkle_column_accumulator(cp, total, pieces):
+    assert sum(pieces) == total
+    rng = np.random.default_rng(total)
+    n = 77
+    a = rnd_field(rng, (total, n))
+    acc = cp.MerkleColumnAccumulator(n, total)
+    t = dev(a)
+    off = 0
+    for k in pieces:
+        acc.update(t[off:off + k])
+        off += k
+    acc.update(t[:0])
+    assert np.array_equal(acc.finalize().cpu().numpy(), oracle.hash_columns(a))
+    with pytest.raises(AssertionError):
+        cp.MerkleColumnAccumulator(n, 128)
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 5, 8, 1000, 1024, 4097])
+def test_merkle_vs_oracle(cp, n):
+    rng = np.random.default_rng(n)
+    leaves = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    root, levels = cp.merkle_build_blake3(torch.from_numpy(leaves).cuda())
+    want = oracle.merkle_levels(leaves)
+    assert len(levels) == len(want)
+    for a, b in zip(levels, want):
+        assert np.array_equal(a.cpu().numpy(), b)
+    assert root.cpu().numpy().tobytes() == want[-1].tobytes()
+    if n % 2 == 0 and n >= 2:
+        one = cp._ensure_compiled().merkle_one_level(torch.from_numpy(leaves).cuda().view(torch.uint32))
+        assert np.array_equal(one.view(torch.uint8).cpu().numpy(), want[1])
+
+
+def test_prg_and_challenge(cp, golden):
+    g = golden.hash_vectors
+    seed = torch.from_numpy(g["chal_seed"].copy()).cuda()
+    got = cp.row_prg_indexed(seed, dev(g["prg_rows"]), 9)
+    assert np.array_equal(host(got), g["prg"])
+    assert np.array_equal(host(cp.row_prg(seed, 0, 3, 9)), g["prg"][:3])
+    assert np.array_equal(host(cp.row_prg(seed, 1000, 1, 9)), g["prg"][3:4])
+    assert tuple(cp.row_prg(seed, 0, 0, 9).shape) == (0, 9) and tuple(cp.row_prg(seed, 0, 4, 0).shape) == (4, 0)
+    big = host(cp.row_prg(seed, 5, 37, 1000))
+    assert np.array_equal(big, oracle.row_prg(g["chal_seed"].tobytes(), 5, 37, 1000))
+    for label in ("", "lin", "irs", "quad"):
+        lab = torch.tensor(list(label.encode()), dtype=torch.uint8, device="cuda")
+        got = cp.challenge_at(seed, lab, dev(g["chal_cids"]))
+        assert np.array_equal(host(got), g[f"chal_{label or 'none'}"])
+        vec = host(cp.challenge_vec(seed, lab, 300))
+        assert [int(v) for v in vec[:3]] == [int(v) for v in g[f"chal_{label or 'none'}"][:3]]
+        assert int(vec[255]) == int(g[f"chal_{label or 'none'}"][3])
+    lab8 = torch.tensor(list(b"abcdefgh"), dtype=torch.uint8, device="cuda")
+    v = host(cp.challenge_vec(seed, lab8, 5))
+    assert [int(x) for x in v] == [oracle.challenge(g["chal_seed"].tobytes(), i, b"abcdefgh") for i in range(5)]
+    assert cp.challenge_vec(seed, lab8, 0).numel() == 0
+
+
+# ---------------------------------------------------------------- K-quant ----
+@pytest.mark.parametrize("qt", ["Q4_K", "Q5_K", "Q6_K"])
+def test_kquant_golden_and_oracle(golden, qt):
+    from verinf_b200 import kquant_cuda as kq
+    g = golden.kquant_vectors
+    S = int(g["S"][0])
+    got = kq.kquant_to_field(torch.from_numpy(g[f"raw_{qt}"].copy()).cuda(), qt, S)
+    assert np.array_equal(host(got), g[f"field_{qt}"])
+    rng = np.random.default_rng(11)
+    nb = 3001
+    raw = synth_blocks(rng, qt, nb)
+    got = kq.kquant_to_field(torch.from_numpy(raw).cuda(), qt, S)
+    assert np.array_equal(host(got), oracle.kquant_to_field(raw, qt, S))
+    assert kq.kquant_to_field(torch.empty(0, dtype=torch.uint8, device="cuda"), qt, S).numel() == 0
+    with pytest.raises(RuntimeError):
+        kq.kquant_to_field(torch.zeros(100, dtype=torch.uint8, device="cuda"), qt, S)
+
+
+def synth_blocks(rng, qt, nb):
+    nbytes = oracle.BLOCK_BYTES[qt]
+    raw = rng.integers(0, 256, size=(nb, nbytes), dtype=np.uint8)
+    d = np.clip(rng.normal(0, 0.02, size=nb), -6e4, 6e4).astype(np.float16)
+    dm = np.clip(rng.normal(0, 0.02, size=nb), -6e4, 6e4).astype(np.float16)
+    if qt == "Q6_K":
+        raw[:, 208:210] = d.view(np.uint8).reshape(nb, 2)
+    else:
+        raw[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+        raw[:, 2:4] = dm.view(np.uint8).reshape(nb, 2)
+    return raw
+
+
+@pytest.mark.parametrize("qt", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("transpose", [True, False])
+def test_kquant_fused_encode(cp, qt, transpose):
+    """fused lift+encode == kquant_to_field -> (transpose) -> row packing -> encode (with PRG pad)"""
+    from verinf_b200 import kquant_cuda as kq
+    rng = np.random.default_rng(23)
+    d_out, d_in, ell, k, n = 96, 512, 1000, 2048, 8192
+    raw = synth_blocks(rng, qt, d_out * d_in // 256)
+    S = 1 << 12
+    lifted = oracle.kquant_to_field(raw, qt, S).reshape(d_out, d_in)
+    flat = (lifted.T if transpose else lifted).reshape(-1)
+    rows = (flat.size + ell - 1) // ell
+    msg = np.zeros(rows * ell, dtype=np.uint64)
+    msg[:flat.size] = flat
+    msg = msg.reshape(rows, ell)
+    seed = bytes(range(7, 39))
+    seed_t = torch.tensor(list(seed), dtype=torch.uint8, device="cuda")
+    want_p, want_c = cp.encode_rows(dev(msg), k, n, master_seed=seed_t, row_offset=5)
+    padded = np.zeros((rows, k), dtype=np.uint64)
+    padded[:, :ell] = msg
+    padded[:, ell:] = oracle.row_prg(seed, 5, rows, k - ell)
+    _, oc = oracle.encode_rows(padded[:3], n)
+    assert np.array_equal(host(want_c)[:3], oc)
+    p, c = kq.kquant_encode_rows(torch.from_numpy(raw).cuda(), qt, S, d_out, d_in, ell=ell, k_deg=k, n_lig=n,
+                                 transpose=transpose, master_seed=seed_t, row_offset=5, need_polys=True)
+    assert torch.equal(c.view(torch.int64), want_c.view(torch.int64))
+    assert torch.equal(p.view(torch.int64), want_p.view(torch.int64))
+    p2, c2 = kq.kquant_encode_rows(torch.from_numpy(raw).cuda(), qt, S, d_out, d_in, ell=ell, k_deg=k, n_lig=n,
+                                   transpose=transpose, first_row=7, n_rows=9, master_seed=seed_t, row_offset=12)
+    assert p2 is None and torch.equal(c2.view(torch.int64), want_c[7:16].view(torch.int64))
+
+
+# ---------------------------------------------------------------- sumcheck ---
+def _terms_from(g, name):
+    terms = []
+    for row in g[f"{name}_terms"]:
+        vals = [int(v) for v in row]
+        terms.append((vals[0], [v for v in vals[1:] if v >= 0]))
+    return terms
+
+
+@pytest.mark.parametrize("name", ["deg3_n6", "deg2_n4", "terms_n6", "mixed_n8", "single_n1"])
+def test_sumcheck_golden(golden, name):
+    from verinf_b200 import layergkr_gpu as lg
+    g = golden.sumcheck_vectors
+    tabs = g[f"{name}_tables"]
+    coins = [int(c) for c in g[f"{name}_coins"]]
+    dts = [dev(t) for t in tabs]
+    terms = [(c, [dts[i] for i in idx]) for c, idx in _terms_from(g, name)]
+    claim, polys, chals, mu = lg.prove_terms_gpu(terms, lambda i: coins[i])
+    assert claim == int(g[f"{name}_claim"][0])
+    assert [[y for _, y in rp] for rp in polys] == [[int(v) for v in row] for row in g[f"{name}_polys"]]
+    assert [[x for x, _ in rp] for rp in polys] == [list(range(len(rp))) for rp in polys]
+    assert chals == coins and mu == 0
+    # python-list factors (the reference's calling convention) give the same transcript
+    terms_l = [(c, [[int(v) for v in tabs[i]] for i in idx]) for c, idx in _terms_from(g, name)]
+    claim2, polys2, _, _ = lg.prove_terms_gpu(terms_l, lambda i: coins[i])
+    assert claim2 == claim and polys2 == polys
+
+
+@pytest.mark.parametrize("logn,terms", [(12, [(1, [0, 1, 2])]), (16, [(1, [0, 1, 2])]), (13, [(3, [0, 1]), (P - 1, [2])]),
+                                        (10, [(1, [0, 1, 2, 3])]), (15, [(1, [0, 0])]), (11, [(2, [1, 0, 2])])])
+def test_sumcheck_vs_oracle(logn, terms):
+    from verinf_b200 import layergkr_gpu as lg
+    rng = np.random.default_rng(logn)
+    ntab = 1 + max(max(f) for _, f in terms)
+    tabs = rnd_field(rng, (ntab, 1 << logn))
+    coins = [int(c) for c in rnd_field(rng, logn)]
+    claim, samples, finals = oracle.sumcheck(tabs, terms, coins)
+    prob = lg.SumcheckProblem(dev(tabs), terms)
+    assert prob.claim() == claim
+    r = None
+    for rnd in range(logn):
+        ys = prob.round(r)
+        assert ys == [int(v) for v in samples[rnd][:len(ys)]], rnd
+        r = coins[rnd]
+    assert prob.round(r) is None
+    assert prob.finals() == [int(v) for v in finals]
+
+
+# ---------------------------------------------------------------- misc ops ---
+def test_linear_algebra(cp):
+    rng = np.random.default_rng(5)
+    A, B = rnd_field(rng, (37, 65)), rnd_field(rng, (65, 41))
+    C = host(cp.gl_matmul(dev(A), dev(B)))
+    for (i, j) in ((0, 0), (36, 40), (17, 3)):
+        assert int(C[i, j]) == sum(int(A[i, l]) * int(B[l, j]) for l in range(65)) % P
+    v = rnd_field(rng, 65)
+    w = host(cp.gl_matvec(dev(A), dev(v)))
+    assert [int(x) for x in w] == [sum(int(a) * int(b) for a, b in zip(A[i], v)) % P for i in range(37)]
+    # CSR
+    n_rows, n_cols = 9, 20
+    row_ptr, col_idx, vals = [0], [], []
+    for _ in range(n_rows):
+        k = int(rng.integers(0, 6))
+        col_idx += [int(c) for c in rng.integers(0, n_cols, size=k)]
+        vals += [int(x) for x in rnd_field(rng, k)]
+        row_ptr.append(len(col_idx))
+    x = rnd_field(rng, n_cols)
+    y = host(cp.gl_spmv(dev(vals), dev(col_idx), dev(row_ptr), dev(x), n_rows))
+    for i in range(n_rows):
+        s = sum(vals[p] * int(x[col_idx[p]]) for p in range(row_ptr[i], row_ptr[i + 1])) % P
+        assert int(y[i]) == s
+    seed = bytes(range(32))
+    seed_t = torch.tensor(list(seed), dtype=torch.uint8, device="cuda")
+    lab = torch.tensor(list(b"lin"), dtype=torch.uint8, device="cuda")
+    y2 = host(cp.gl_spmv_challenged(dev(vals), dev(col_idx), dev(row_ptr), seed_t, lab, n_rows))
+    for i in range(n_rows):
+        s = sum(vals[p] * oracle.challenge(seed, col_idx[p], b"lin") for p in range(row_ptr[i], row_ptr[i + 1])) % P
+        assert int(y2[i]) == s
+
+
+def test_lookup_multiplicities(cp):
+    x = dev([0, 3, 3, 7, 9, 100, 3])
+    table = dev(list(range(8)))
+    m = host(cp.lookup_multiplicities(x, table))
+    assert [int(v) for v in m] == [1, 0, 0, 3, 0, 0, 0, 1]
+    acc = torch.zeros(8, dtype=torch.uint64, device="cuda")
+    cp.lookup_multiplicities_into(x, table, acc)
+    cp.lookup_multiplicities_into(x, table, acc)
+    assert [int(v) for v in host(acc)] == [2, 0, 0, 6, 0, 0, 0, 2]
+    t2 = dev([5, 9, 100, 3])
+    acc2 = torch.zeros(4, dtype=torch.uint64, device="cuda")
+    cp.lookup_multiplicities_into(x, t2, acc2)
+    assert [int(v) for v in host(acc2)] == [0, 1, 1, 3]
+
+
+def test_interp_bands(cp):
+    seed = bytes(range(32))
+    seed_t = torch.tensor(list(seed), dtype=torch.uint8, device="cuda")
+    lab = torch.tensor(list(b"lin"), dtype=torch.uint8, device="cuda")
+    ch = lambda c: oracle.challenge(seed, c, b"lin")   # noqa: E731
+    n = 24
+    out = torch.zeros(n + 4, dtype=torch.uint64, device="cuda")
+    # causal_id: base, m, h, coef
+    cp.interp_band_causal_id(out, 2, 5, n, 1000, 4, 3, 11, seed_t, lab)
+    got = host(out)
+    for s in range(n):
+        f = 5 + s
+        b, j = divmod(f, 4)
+        iq, hh = divmod(b, 3)
+        want = 0 if j > iq else 11 * ch(1000 + 3 * iq * (iq + 1) // 2 + hh * (iq + 1) + j) % P
+        assert int(got[2 + s]) == want
+    assert not got[:2].any() and not got[2 + n:].any()
+    # descriptor band, const coef, PRF challenges, fan 2
+    desc = [0] * 24
+    desc[0] = 2; desc[1] = 1; desc[2] = 5; desc[5] = 70; desc[6] = 10; desc[7] = 1
+    desc[10] = 2; desc[11] = 100; desc[12] = 0; desc[13] = 9
+    out2 = torch.zeros(n, dtype=torch.uint64, device="cuda")
+    z = torch.zeros(1, dtype=torch.uint64, device="cuda")
+    cp.interp_band(out2, 0, 3, n, dev(desc), z, z, z, seed_t, lab)
+    got2 = host(out2)
+    for s in range(n):
+        hi, lo = divmod(3 + s, 5)
+        cid = 70 + hi * 10 + lo
+        assert int(got2[s]) == 9 * ((ch(cid) + ch(cid + 100)) % P) % P

@@ -1,0 +1,337 @@
+// Elementwise Goldilocks ops and the non-hot-path exports of the reference module
+// (poly_eval, dense/sparse mat-vec, lookup multiplicities, q_lin band interpreters).
+//
+// Replaces k_gl_mul/add/sub/pow (prover/cuda_primitives.py:208-223), k_neg /
+// k_axpy_inplace / k_poly_eval / k_lookup_multiplicities(_range)
+// (prover/kernels/gl_extras.cuh), k_matmul / k_matvec (prover/kernels/gl_matmul.cuh),
+// k_spmv / k_spmv_challenged (prover/kernels/gl_spmv.cuh) and the k_interp_band /
+// k_band_* kernels (prover/cuda_primitives.py:605-734).  All indexing is 64-bit.
+#include "../../include/verinf_b200.h"
+#include "blake3.cuh"
+#include "common.cuh"
+#include "gl.cuh"
+
+namespace {
+
+using vgl::add;
+using vgl::mul;
+using vgl::sub;
+
+constexpr int BLOCK = 256;
+inline unsigned grid_for(int64_t n, int per_thread = 1) {
+    int64_t g = (n + (int64_t)BLOCK * per_thread - 1) / ((int64_t)BLOCK * per_thread);
+    int64_t cap = 148 * 16;   // grid-stride loops: a few waves over the 148 SMs
+    return (unsigned)(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+template <int OP>
+__device__ __forceinline__ uint64_t apply(uint64_t a, uint64_t b) {
+    return OP == 0 ? mul(a, b) : OP == 1 ? add(a, b) : sub(a, b);
+}
+
+// operands may alias the output (no __restrict__)
+template <int OP>
+__global__ void __launch_bounds__(BLOCK) k_binary_alias(const uint64_t* a, const uint64_t* b, uint64_t* out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride) out[i] = apply<OP>(a[i], b[i]);
+}
+template <int OP>
+__global__ void __launch_bounds__(BLOCK) k_binary_bcast(const uint64_t* a, const uint64_t* __restrict__ b, int64_t nb,
+                                                        uint64_t* out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride) out[i] = apply<OP>(a[i], __ldg(b + i % nb));
+}
+__global__ void __launch_bounds__(BLOCK) k_neg(const uint64_t* a, uint64_t* out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride) out[i] = vgl::neg(a[i]);
+}
+__global__ void __launch_bounds__(BLOCK) k_pow(const uint64_t* a, uint64_t e, uint64_t* out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride) out[i] = vgl::pow(a[i], e);
+}
+__global__ void __launch_bounds__(BLOCK) k_axpy(uint64_t* y, uint64_t alpha, const uint64_t* x, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride) y[i] = add(y[i], mul(alpha, x[i]));
+}
+
+__global__ void k_poly_eval(const uint64_t* __restrict__ coeffs, int64_t m, int64_t d,
+                            const uint64_t* __restrict__ points, int64_t k, uint64_t* __restrict__ out) {
+    const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t r = (int64_t)blockIdx.y * blockDim.y + threadIdx.y;
+    if (p >= k || r >= m) return;
+    const uint64_t x = points[p];
+    const uint64_t* row = coeffs + r * d;
+    uint64_t acc = 0;
+    for (int64_t i = d - 1; i >= 0; --i) acc = add(mul(acc, x), row[i]);
+    out[r * k + p] = acc;
+}
+
+// C = A.B mod p with 32x32 output tiles staged through shared memory.
+__global__ void __launch_bounds__(256) k_matmul(const uint64_t* __restrict__ A, const uint64_t* __restrict__ B,
+                                                uint64_t* __restrict__ C, int64_t m, int64_t k, int64_t n) {
+    __shared__ uint64_t sa[32][33], sb[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8 threads, 4 rows each
+    const int64_t row0 = (int64_t)blockIdx.y * 32, col0 = (int64_t)blockIdx.x * 32;
+    uint64_t acc[4] = {0, 0, 0, 0};
+    for (int64_t l0 = 0; l0 < k; l0 += 32) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            int r = ty + 8 * q;
+            sa[r][tx] = (row0 + r < m && l0 + tx < k) ? A[(row0 + r) * k + l0 + tx] : 0;
+            sb[r][tx] = (l0 + r < k && col0 + tx < n) ? B[(l0 + r) * n + col0 + tx] : 0;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int l = 0; l < 32; ++l) {
+            uint64_t bv = sb[l][tx];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q] = add(acc[q], mul(sa[ty + 8 * q][l], bv));
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        int64_t r = row0 + ty + 8 * q;
+        if (r < m && col0 + tx < n) C[r * n + col0 + tx] = acc[q];
+    }
+}
+
+// w = M.v: one warp per row, lanes stride the row, shuffle reduction.
+__global__ void __launch_bounds__(256) k_matvec(const uint64_t* __restrict__ M, const uint64_t* __restrict__ v,
+                                                uint64_t* __restrict__ w, int64_t m, int64_t n) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (row >= m) return;
+    const uint64_t* r = M + row * n;
+    uint64_t acc = 0;
+    for (int64_t j = lane; j < n; j += 32) acc = add(acc, mul(r[j], __ldg(v + j)));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc = add(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+    if (lane == 0) w[row] = acc;
+}
+
+__global__ void __launch_bounds__(BLOCK) k_spmv(const uint64_t* __restrict__ values, const uint64_t* __restrict__ col_idx,
+                                                const uint64_t* __restrict__ row_ptr, const uint64_t* __restrict__ x,
+                                                const uint8_t* __restrict__ seed, const uint8_t* __restrict__ label,
+                                                int label_len, uint64_t* __restrict__ y, int64_t n_rows) {
+    const int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n_rows) return;
+    uint32_t s[8];
+    uint64_t lab = 0;
+    if (!x) { vb3::load_seed(seed, s); lab = vb3::load_label(label, label_len); }
+    uint64_t acc = 0;
+    for (uint64_t p = row_ptr[i]; p < row_ptr[i + 1]; ++p) {
+        uint64_t xv = x ? x[col_idx[p]] : vb3::challenge(s, lab, label_len, col_idx[p]);
+        acc = add(acc, mul(values[p], xv));
+    }
+    y[i] = acc;
+}
+
+__global__ void __launch_bounds__(BLOCK) k_lookup(const uint64_t* __restrict__ x, int64_t n_x,
+                                                  const uint64_t* __restrict__ table, int64_t n_table,
+                                                  unsigned long long* __restrict__ mult) {
+    const int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (i >= n_x) return;
+    const uint64_t xi = x[i];
+    if (!table) {
+        if (xi < (uint64_t)n_table) atomicAdd(&mult[xi], 1ULL);
+        return;
+    }
+    for (int64_t j = 0; j < n_table; ++j)
+        if (__ldg(table + j) == xi) { atomicAdd(&mult[j], 1ULL); return; }
+}
+
+struct BandArgs {
+    int kind;
+    uint64_t* out;
+    int64_t out_off, flat_lo, n_slots;
+    uint64_t p0, p1, p2, p3;
+    const uint64_t* desc;
+    const void* aux0;
+    const void* aux1;
+    const uint64_t* chal_buf;
+    int64_t aux_n;
+    const uint8_t* seed;
+    const uint8_t* label;
+    int label_len;
+};
+
+__global__ void __launch_bounds__(BLOCK) k_band(BandArgs a) {
+    const int64_t s = (int64_t)blockIdx.x * BLOCK + threadIdx.x;
+    if (s >= a.n_slots) return;
+    uint32_t sd[8];
+    vb3::load_seed(a.seed, sd);
+    const uint64_t lab = vb3::load_label(a.label, a.label_len);
+    auto chal = [&](uint64_t cid) { return vb3::challenge(sd, lab, a.label_len, cid); };
+    uint64_t* o = a.out + a.out_off + s;
+    const uint64_t f = (uint64_t)a.flat_lo + (uint64_t)s;
+    if (a.kind == 0) {
+        const uint64_t* d = a.desc;
+        const uint64_t* tblA = (const uint64_t*)a.aux0;
+        const uint64_t* tblB = (const uint64_t*)a.aux1;
+        uint64_t rem = f;
+        int q = (int)d[0];
+        uint64_t cid = d[5], ia = 0, ib = 0;
+        for (int j = q - 1; j >= 1; --j) {
+            uint64_t dig = rem % d[1 + j];
+            rem /= d[1 + j];
+            cid += dig * d[6 + j]; ia += dig * d[14 + j]; ib += dig * d[18 + j];
+        }
+        cid += rem * d[6]; ia += rem * d[14]; ib += rem * d[18];
+        uint64_t mode = d[12];
+        uint64_t coef = mode == 0 ? d[13] : mode == 1 ? tblA[ia] : sub(0, mul(tblA[ia], tblB[ib]));
+        uint64_t fan = d[10], fs = d[11], acc = 0;
+        for (uint64_t t = 0; t < fan; ++t) {
+            uint64_t c = cid + t * fs;
+            acc = add(acc, d[22] ? a.chal_buf[c - d[23]] : chal(c));
+        }
+        *o = add(*o, mul(coef, acc));
+    } else if (a.kind == 1) {
+        uint64_t base = a.p0, m = a.p1, h = a.p2, coef = a.p3;
+        uint64_t b = f / m, j = f % m, iq = b / h, hh = b % h;
+        if (j > iq) return;
+        uint64_t cid = base + h * iq * (iq + 1) / 2 + hh * (iq + 1) + j;
+        *o = add(*o, mul(coef, chal(cid)));
+    } else if (a.kind == 2) {
+        uint64_t base = a.p0, h = a.p1, coef = a.p2;
+        uint64_t iq = f / h, hh = f % h;
+        uint64_t rank0 = base + h * iq * (iq + 1) / 2 + hh * (iq + 1), acc = 0;
+        for (uint64_t jo = 0; jo <= iq; ++jo) acc = add(acc, chal(rank0 + jo));
+        *o = add(*o, mul(coef, acc));
+    } else if (a.kind == 3) {
+        uint64_t base = a.p0, d = a.p1, rows_per_w = a.p2, ell = a.p3;
+        const int64_t* tok = (const int64_t*)a.aux0;
+        uint64_t row_off = f / ell, within = f % ell, rel = within / d, jj = within % d;
+        if (rel >= rows_per_w) return;
+        int64_t v = (int64_t)(row_off * rows_per_w + rel);
+        uint64_t acc = 0;
+        for (int64_t i = 0; i < a.aux_n; ++i)
+            if (tok[i] == v) acc = add(acc, chal(base + (uint64_t)i * d + jj));
+        *o = add(*o, sub(0, acc));
+    } else {
+        uint64_t base = a.p0, H = a.p1, d_h = a.p2, half = d_h / 2;
+        const uint64_t* cos_t = (const uint64_t*)a.aux0;
+        const uint64_t* sin_t = (const uint64_t*)a.aux1;
+        uint64_t sq = f / (H * d_h), hh = (f / d_h) % H, k = f % d_h, e = k / half, kp = k % half;
+        uint64_t pair_t = sq * H * half + hh * half + kp, ci = sq * half + kp;
+        uint64_t c = cos_t[ci], sn = sin_t[ci];
+        uint64_t r1 = chal(base + 2 * pair_t), r2 = chal(base + 2 * pair_t + 1);
+        uint64_t c1 = e == 0 ? sub(0, c) : sn;
+        uint64_t c2 = e == 0 ? sub(0, sn) : sub(0, c);
+        *o = add(*o, add(mul(c1, r1), mul(c2, r2)));
+    }
+}
+
+}  // namespace
+
+#define VI_LAUNCH_1D(kernel, n, ...)                                                        \
+    do {                                                                                    \
+        if ((n) > 0) kernel<<<grid_for(n), BLOCK, 0, (cudaStream_t)stream>>>(__VA_ARGS__);  \
+        return vi::check_launch(#kernel);                                                   \
+    } while (0)
+
+extern "C" int vi_gl_binary(int op, const uint64_t* a, const uint64_t* b, uint64_t* out, int64_t n, void* stream) {
+    VI_REQUIRE(op >= 0 && op <= 2, "gl_binary: op must be 0 (mul), 1 (add) or 2 (sub)");
+    VI_REQUIRE(n >= 0, "gl_binary: negative size");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(a && b && out, "gl_binary: null pointer");
+    if (op == 0) VI_LAUNCH_1D(k_binary_alias<0>, n, a, b, out, n);
+    if (op == 1) VI_LAUNCH_1D(k_binary_alias<1>, n, a, b, out, n);
+    VI_LAUNCH_1D(k_binary_alias<2>, n, a, b, out, n);
+}
+
+extern "C" int vi_gl_binary_bcast(int op, const uint64_t* a, const uint64_t* b, int64_t nb, uint64_t* out, int64_t n, void* stream) {
+    VI_REQUIRE(op >= 0 && op <= 2, "gl_binary_bcast: op must be 0 (mul), 1 (add) or 2 (sub)");
+    VI_REQUIRE(n >= 0 && nb > 0, "gl_binary_bcast: bad size");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(a && b && out, "gl_binary_bcast: null pointer");
+    if (op == 0) VI_LAUNCH_1D(k_binary_bcast<0>, n, a, b, nb, out, n);
+    if (op == 1) VI_LAUNCH_1D(k_binary_bcast<1>, n, a, b, nb, out, n);
+    VI_LAUNCH_1D(k_binary_bcast<2>, n, a, b, nb, out, n);
+}
+
+extern "C" int vi_gl_neg(const uint64_t* a, uint64_t* out, int64_t n, void* stream) {
+    VI_REQUIRE(n >= 0, "gl_neg: negative size");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(a && out, "gl_neg: null pointer");
+    VI_LAUNCH_1D(k_neg, n, a, out, n);
+}
+extern "C" int vi_gl_pow(const uint64_t* base, uint64_t exp, uint64_t* out, int64_t n, void* stream) {
+    VI_REQUIRE(n >= 0, "gl_pow: negative size");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(base && out, "gl_pow: null pointer");
+    VI_LAUNCH_1D(k_pow, n, base, exp, out, n);
+}
+extern "C" int vi_gl_axpy(uint64_t* y, uint64_t alpha, const uint64_t* x, int64_t n, void* stream) {
+    VI_REQUIRE(n >= 0, "gl_axpy: negative size");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(y && x, "gl_axpy: null pointer");
+    VI_LAUNCH_1D(k_axpy, n, y, alpha, x, n);
+}
+
+extern "C" int vi_poly_eval(const uint64_t* coeffs, int64_t m, int64_t d, const uint64_t* points, int64_t k,
+                            uint64_t* out, void* stream) {
+    VI_REQUIRE(m >= 0 && d >= 0 && k >= 0, "poly_eval: negative size");
+    if (m == 0 || k == 0) return VI_OK;
+    dim3 block(64, 4), grid((unsigned)((k + 63) / 64), (unsigned)((m + 3) / 4));
+    VI_REQUIRE(grid.y <= 65535, "poly_eval: too many rows for one launch");
+    k_poly_eval<<<grid, block, 0, (cudaStream_t)stream>>>(coeffs, m, d, points, k, out);
+    return vi::check_launch("k_poly_eval");
+}
+
+extern "C" int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n, void* stream) {
+    VI_REQUIRE(m >= 0 && k >= 0 && n >= 0, "gl_matmul: negative size");
+    if (m == 0 || n == 0) return VI_OK;
+    dim3 grid((unsigned)((n + 31) / 32), (unsigned)((m + 31) / 32));
+    VI_REQUIRE(grid.y <= 65535, "gl_matmul: too many rows for one launch (m <= 2097120)");
+    k_matmul<<<grid, 256, 0, (cudaStream_t)stream>>>(A, B, C, m, k, n);
+    return vi::check_launch("k_matmul");
+}
+
+extern "C" int vi_gl_matvec(const uint64_t* M, const uint64_t* v, uint64_t* w, int64_t m, int64_t n, void* stream) {
+    VI_REQUIRE(m >= 0 && n >= 0, "gl_matvec: negative size");
+    if (m == 0) return VI_OK;
+    int64_t grid = (m * 32 + 255) / 256;
+    VI_REQUIRE(grid <= 0x7FFFFFFFLL, "gl_matvec: too many rows");
+    k_matvec<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(M, v, w, m, n);
+    return vi::check_launch("k_matvec");
+}
+
+extern "C" int vi_gl_spmv(const uint64_t* values, const uint64_t* col_idx, const uint64_t* row_ptr,
+                          const uint64_t* x, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
+                          uint64_t* y, int64_t n_rows, void* stream) {
+    VI_REQUIRE(n_rows >= 0, "gl_spmv: negative size");
+    VI_REQUIRE(x || (seed_dev && label_len >= 0 && label_len <= 8), "gl_spmv: need x or (seed, label<=8)");
+    if (n_rows == 0) return VI_OK;
+    int64_t grid = (n_rows + BLOCK - 1) / BLOCK;
+    k_spmv<<<(unsigned)grid, BLOCK, 0, (cudaStream_t)stream>>>(values, col_idx, row_ptr, x, seed_dev, label_dev,
+                                                             label_len, y, n_rows);
+    return vi::check_launch("k_spmv");
+}
+
+extern "C" int vi_lookup_multiplicities(const uint64_t* x, int64_t n_x, const uint64_t* table, int64_t n_table,
+                                        uint64_t* mult, void* stream) {
+    VI_REQUIRE(n_x >= 0 && n_table >= 0, "lookup: negative size");
+    if (n_x == 0) return VI_OK;
+    int64_t grid = (n_x + BLOCK - 1) / BLOCK;
+    VI_REQUIRE(grid <= 0x7FFFFFFFLL, "lookup: too many elements");
+    k_lookup<<<(unsigned)grid, BLOCK, 0, (cudaStream_t)stream>>>(x, n_x, table, n_table, (unsigned long long*)mult);
+    return vi::check_launch("k_lookup");
+}
+
+extern "C" int vi_interp_band(int kind, uint64_t* out, int64_t out_off, int64_t flat_lo, int64_t n_slots,
+                              uint64_t p0, uint64_t p1, uint64_t p2, uint64_t p3,
+                              const uint64_t* desc_dev, const void* aux0, const void* aux1, const uint64_t* chal_buf,
+                              int64_t aux_n, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
+                              void* stream) {
+    VI_REQUIRE(kind >= 0 && kind <= 4, "interp_band: unknown kind %d", kind);
+    VI_REQUIRE(n_slots >= 0, "interp_band: negative size");
+    VI_REQUIRE(label_len >= 0 && label_len <= 8, "interp_band: label must be <= 8 bytes");
+    if (n_slots == 0) return VI_OK;
+    BandArgs a{kind, out, out_off, flat_lo, n_slots, p0, p1, p2, p3, desc_dev, aux0, aux1, chal_buf, aux_n,
+               seed_dev, label_dev, label_len};
+    int64_t grid = (n_slots + BLOCK - 1) / BLOCK;
+    VI_REQUIRE(grid <= 0x7FFFFFFFLL, "interp_band: too many slots");
+    k_band<<<(unsigned)grid, BLOCK, 0, (cudaStream_t)stream>>>(a);
+    return vi::check_launch("k_band");
+}

@@ -75,7 +75,6 @@ __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
     }
 }
 
-#ifndef __CUDA_ARCH__
 // host-side helpers used when building twiddle tables
 inline uint64_t hmul(uint64_t a, uint64_t b) {
     unsigned __int128 v = (unsigned __int128)a * b;
@@ -86,6 +85,5 @@ inline uint64_t hpow(uint64_t b, uint64_t e) {
     while (e) { if (e & 1) r = hmul(r, b); b = hmul(b, b); e >>= 1; }
     return r;
 }
-#endif
 
 }  // namespace vgl

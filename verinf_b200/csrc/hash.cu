@@ -1,0 +1,243 @@
+// BLAKE3 column hashing, Merkle levels, pad PRG and challenge PRF for sm_100a.
+//
+// Replaces prover/kernels/blake3_columns.cuh (k_hash_columns_simple, k_stream_*),
+// prover/kernels/merkle.cuh (k_level), k_row_prg(_indexed) and k_challenge_vec/_at
+// (prover/cuda_primitives.py:566-591,796-1004).
+//
+// Column hash design: all columns advance in lockstep, so the BLAKE3 chunk counter
+// and the shape of the chaining-value stack are the same for every column and live
+// on the host.  The device state is only the stack contents, indexed by subtree
+// size instead of by a stack pointer: level b holds the chaining value of a
+// complete subtree of 2^b chunks (the binary-counter form of BLAKE3's incremental
+// tree), stored [level][word][column] so every access is coalesced.
+#include "../../include/verinf_b200.h"
+#include "blake3.cuh"
+#include "common.cuh"
+#include "gl.cuh"
+
+namespace {
+
+constexpr int CHUNK_ROWS = 128;   // 1024-byte BLAKE3 chunk = 128 field elements
+
+struct StreamArgs {
+    const uint64_t* rows;   // first row of this call, row-major, leading dimension ncols
+    int64_t ncols;
+    int64_t n_rows;         // rows in this call
+    uint64_t count0;        // chunks hashed before this call
+    uint64_t total_chunks;  // chunks of the whole stream (>= 1)
+    uint32_t* state;        // [level][8][ncols]
+    uint32_t* digests;      // (ncols, 8) words; written by the call that ends the stream
+};
+
+__global__ void __launch_bounds__(128) k_hash_stream(StreamArgs a) {
+    const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= a.ncols) return;
+    const uint64_t* p = a.rows + col;
+    const int64_t ld = a.ncols;
+    const int64_t n_chunks = a.n_rows == 0 ? 1 : (a.n_rows + CHUNK_ROWS - 1) / CHUNK_ROWS;
+    const bool single = a.total_chunks == 1;
+
+    for (int64_t ch = 0; ch < n_chunks; ++ch) {
+        const uint64_t count = a.count0 + (uint64_t)ch;           // = this chunk's counter
+        int64_t r0 = ch * CHUNK_ROWS;
+        int64_t rows_here = a.n_rows - r0 < CHUNK_ROWS ? a.n_rows - r0 : CHUNK_ROWS;
+        int nb = rows_here == 0 ? 1 : (int)((rows_here + 7) / 8);
+        uint32_t cv[8];
+        vb3::set_iv(cv);
+        for (int b = 0; b < nb; ++b) {
+            int64_t rb = rows_here - b * 8 < 8 ? rows_here - b * 8 : 8;
+            uint32_t m[16];
+            const uint64_t* q = p + (r0 + b * 8) * ld;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                uint64_t x = r < rb ? __ldg(q + r * ld) : 0;
+                m[2 * r] = (uint32_t)x;
+                m[2 * r + 1] = (uint32_t)(x >> 32);
+            }
+            uint32_t flags = (b == 0 ? vb3::CHUNK_START : 0) |
+                             (b == nb - 1 ? (vb3::CHUNK_END | (single ? vb3::ROOT : 0)) : 0);
+            vb3::compress(cv, m, count, (uint32_t)(rb * 8), flags);
+        }
+        const bool is_final = count + 1 == a.total_chunks;
+        if (!is_final) {
+            // binary-counter carry: merge with every complete subtree whose bit is set
+            int b = 0;
+            while ((count >> b) & 1) {
+                uint32_t l[8], o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) l[i] = a.state[((int64_t)b * 8 + i) * a.ncols + col];
+                vb3::parent(l, cv, 0, o);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) cv[i] = o[i];
+                ++b;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a.state[((int64_t)b * 8 + i) * a.ncols + col] = cv[i];
+        } else {
+            // close the tree: fold in the pending subtrees, smallest first; the last merge is the root
+            uint64_t rem = count;
+            int b = 0;
+            while (rem) {
+                if (rem & 1) {
+                    uint32_t l[8], o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) l[i] = a.state[((int64_t)b * 8 + i) * a.ncols + col];
+                    vb3::parent(l, cv, (rem >> 1) == 0 ? vb3::ROOT : 0, o);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) cv[i] = o[i];
+                }
+                rem >>= 1;
+                ++b;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a.digests[col * 8 + i] = cv[i];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) k_merkle_level(const uint32_t* __restrict__ in, int64_t n_in,
+                                                      uint32_t* __restrict__ out, int64_t n_out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_out) return;
+    const int64_t li = 2 * i, ri = (2 * i + 1 < n_in) ? 2 * i + 1 : 2 * i;
+    uint32_t m[16], h[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { m[k] = __ldg(in + li * 8 + k); m[8 + k] = __ldg(in + ri * 8 + k); }
+    vb3::hash_one_block(m, 64, h);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[i * 8 + k] = h[k];
+}
+
+__global__ void __launch_bounds__(256) k_row_prg(const uint8_t* __restrict__ seed, int64_t row_off,
+                                                 const uint64_t* __restrict__ rows, int64_t n_rows,
+                                                 int64_t slack, uint64_t* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * slack) return;
+    const int64_t r = i / slack, k = i - r * slack;
+    uint32_t s[8];
+    vb3::load_seed(seed, s);
+    const uint64_t row = rows ? rows[r] : (uint64_t)(row_off + r);
+    out[i] = vb3::pad_prg(s, row, (uint64_t)k);
+}
+
+__global__ void __launch_bounds__(256) k_challenge(const uint8_t* __restrict__ seed,
+                                                   const uint8_t* __restrict__ label, int label_len,
+                                                   const uint64_t* __restrict__ cids, int64_t n,
+                                                   uint64_t* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t s[8];
+    vb3::load_seed(seed, s);
+    out[i] = vb3::challenge(s, vb3::load_label(label, label_len), label_len, cids ? cids[i] : (uint64_t)i);
+}
+
+int state_levels(int64_t total_chunks) {
+    int b = 1;
+    while ((int64_t(1) << b) < total_chunks) ++b;
+    return b + 1;
+}
+
+}  // namespace
+
+extern "C" int64_t vi_hash_stream_state_bytes(int64_t ncols, int64_t total_rows) {
+    if (ncols <= 0) return 0;
+    int64_t chunks = total_rows <= 0 ? 1 : (total_rows + CHUNK_ROWS - 1) / CHUNK_ROWS;
+    return (int64_t)state_levels(chunks) * 32 * ncols;
+}
+
+extern "C" int vi_hash_stream_update(void* state, int64_t ncols, int64_t total_rows, int64_t rows_done,
+                                     const uint64_t* rows, int64_t n_rows, uint8_t* digests, void* stream) {
+    VI_REQUIRE(ncols >= 0 && total_rows >= 0 && rows_done >= 0 && n_rows >= 0, "hash stream: negative size");
+    VI_REQUIRE(rows_done + n_rows <= total_rows, "hash stream: more rows than announced (%lld + %lld > %lld)",
+               (long long)rows_done, (long long)n_rows, (long long)total_rows);
+    VI_REQUIRE(rows_done % CHUNK_ROWS == 0, "hash stream: rows_done must be a multiple of 128");
+    const bool ends = rows_done + n_rows == total_rows;
+    VI_REQUIRE(ends || n_rows % CHUNK_ROWS == 0, "hash stream: only the last call may bring a partial chunk");
+    if (ncols == 0) return VI_OK;
+    if (n_rows == 0 && !(ends && total_rows == 0)) return VI_OK;
+    VI_REQUIRE(state != nullptr, "hash stream: null state");
+    VI_REQUIRE(!ends || digests != nullptr, "hash stream: the closing call needs a digest buffer");
+    VI_REQUIRE(n_rows == 0 || rows != nullptr, "hash stream: null rows");
+    StreamArgs a;
+    a.rows = rows; a.ncols = ncols; a.n_rows = n_rows;
+    a.count0 = (uint64_t)(rows_done / CHUNK_ROWS);
+    a.total_chunks = total_rows == 0 ? 1 : (uint64_t)((total_rows + CHUNK_ROWS - 1) / CHUNK_ROWS);
+    a.state = (uint32_t*)state; a.digests = (uint32_t*)digests;
+    const int block = 128;
+    k_hash_stream<<<(unsigned)((ncols + block - 1) / block), block, 0, (cudaStream_t)stream>>>(a);
+    return vi::check_launch("k_hash_stream");
+}
+
+extern "C" int64_t vi_hash_columns_scratch_bytes(int64_t m, int64_t ncols) {
+    return vi_hash_stream_state_bytes(ncols, m);
+}
+
+extern "C" int vi_hash_columns(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* digests,
+                               void* scratch, int64_t scratch_bytes, void* stream) {
+    VI_REQUIRE(m >= 0 && ncols >= 0, "hash_columns: negative size");
+    if (ncols == 0) return VI_OK;
+    int64_t need = vi_hash_stream_state_bytes(ncols, m);
+    if (m > CHUNK_ROWS && (scratch == nullptr || scratch_bytes < need))
+        return vi::fail(VI_ERR_SCRATCH, "hash_columns: scratch of %lld bytes required", (long long)need);
+    // a single-chunk input never touches the state
+    void* st = m > CHUNK_ROWS ? scratch : (void*)digests;
+    return vi_hash_stream_update(st, ncols, m, 0, mat, m, digests, stream);
+}
+
+extern "C" int64_t vi_merkle_upper_nodes(int64_t n) {
+    int64_t t = 0;
+    while (n > 1) { n = (n + 1) / 2; t += n; }
+    return t;
+}
+
+extern "C" int vi_merkle_level(const uint8_t* nodes, int64_t n_nodes, uint8_t* parents, void* stream) {
+    VI_REQUIRE(n_nodes >= 0, "merkle: negative size");
+    if (n_nodes <= 1) return VI_OK;
+    VI_REQUIRE(nodes && parents, "merkle: null pointer");
+    VI_REQUIRE(((uintptr_t)nodes & 3) == 0 && ((uintptr_t)parents & 3) == 0, "merkle: buffers must be 4-byte aligned");
+    int64_t n_out = (n_nodes + 1) / 2;
+    const int block = 128;
+    k_merkle_level<<<(unsigned)((n_out + block - 1) / block), block, 0, (cudaStream_t)stream>>>(
+        (const uint32_t*)nodes, n_nodes, (uint32_t*)parents, n_out);
+    return vi::check_launch("k_merkle_level");
+}
+
+extern "C" int vi_merkle_build(const uint8_t* leaves, int64_t n, uint8_t* upper, void* stream) {
+    VI_REQUIRE(n >= 0, "merkle: negative size");
+    const uint8_t* cur = leaves;
+    uint8_t* nxt = upper;
+    while (n > 1) {
+        int rc = vi_merkle_level(cur, n, nxt, stream);
+        if (rc) return rc;
+        n = (n + 1) / 2;
+        cur = nxt;
+        nxt += n * 32;
+    }
+    return VI_OK;
+}
+
+extern "C" int vi_row_prg(const uint8_t* seed_dev, int64_t row_off, const uint64_t* rows_dev,
+                          int64_t n_rows, int64_t slack, uint64_t* out, void* stream) {
+    VI_REQUIRE(n_rows >= 0 && slack >= 0, "row_prg: negative size");
+    if (n_rows == 0 || slack == 0) return VI_OK;
+    VI_REQUIRE(seed_dev && out, "row_prg: null pointer");
+    int64_t total = n_rows * slack;
+    const int block = 256;
+    int64_t grid = (total + block - 1) / block;
+    if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "row_prg: too many elements");
+    k_row_prg<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(seed_dev, row_off, rows_dev, n_rows, slack, out);
+    return vi::check_launch("k_row_prg");
+}
+
+extern "C" int vi_challenge(const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
+                            const uint64_t* cids_dev, int64_t n, uint64_t* out, void* stream) {
+    VI_REQUIRE(n >= 0, "challenge: negative size");
+    VI_REQUIRE(label_len >= 0 && label_len <= 8, "challenge: label must be <= 8 bytes");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(seed_dev && out && (label_len == 0 || label_dev), "challenge: null pointer");
+    const int block = 256;
+    int64_t grid = (n + block - 1) / block;
+    if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "challenge: too many elements");
+    k_challenge<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(seed_dev, label_dev, label_len, cids_dev, n, out);
+    return vi::check_launch("k_challenge");
+}

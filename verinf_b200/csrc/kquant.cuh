@@ -1,0 +1,67 @@
+// K-quant (GGUF Q4_K / Q5_K / Q6_K super-block) element decode -> Goldilocks field.
+//
+// Arithmetic contract (prover/kquant_cuda.py:42-111, which mirrors gguf-py's
+// dequantize_blocks): v = (d*sc)*q - (dmin*mn) for Q4_K/Q5_K, v = (d*sc)*q for Q6_K,
+// every fp32 operation rounded separately (the intrinsics below are never fused into
+// an FMA), then ll = round_half_even(double(v) * S) and field = ll >= 0 ? ll : p - |ll|.
+#pragma once
+#include <cuda_fp16.h>
+#include <cstdint>
+
+namespace vkq {
+
+constexpr int Q4_K = 4, Q5_K = 5, Q6_K = 6;
+__host__ __device__ constexpr int block_bytes(int qtype) { return qtype == 4 ? 144 : qtype == 5 ? 176 : 210; }
+
+__device__ __forceinline__ float ld_half(const uint8_t* __restrict__ p) {
+    unsigned short bits = (unsigned short)__ldg(p) | ((unsigned short)__ldg(p + 1) << 8);
+    return __half2float(__ushort_as_half(bits));
+}
+
+__device__ __forceinline__ uint64_t to_field(float v, double S) {
+    long long ll = __double2ll_rn(__dmul_rn((double)v, S));
+    return ll >= 0 ? (uint64_t)ll : 0xFFFFFFFF00000001ull - (uint64_t)(-ll);
+}
+
+// 6-bit (scale, min) of sub-block s in [0,8) from the 12 packed bytes
+__device__ __forceinline__ void scale_min(const uint8_t* __restrict__ s12, int s, uint32_t& sc, uint32_t& mn) {
+    if (s < 4) {
+        sc = __ldg(s12 + s) & 63;
+        mn = __ldg(s12 + s + 4) & 63;
+    } else {
+        uint32_t hi = __ldg(s12 + s + 4);
+        sc = (hi & 0xF) | ((__ldg(s12 + s - 4) >> 6) << 4);
+        mn = (hi >> 4) | ((__ldg(s12 + s) >> 6) << 4);
+    }
+}
+
+// element e (0..255) of the super-block at p
+template <int QT>
+__device__ __forceinline__ uint64_t lift(const uint8_t* __restrict__ p, int e, double S) {
+    if constexpr (QT == Q6_K) {
+        const float d = ld_half(p + 208);
+        int lo = (__ldg(p + (e >> 7) * 64 + (e & 63)) >> (4 * ((e >> 6) & 1))) & 0xF;
+        int hi = (__ldg(p + 128 + (e >> 7) * 32 + (e & 31)) >> (2 * ((e >> 5) & 3))) & 3;
+        int q = (lo | (hi << 4)) - 32;
+        int sc = (int)(signed char)__ldg(p + 192 + (e >> 4));
+        float v = __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+        return to_field(v, S);
+    } else {
+        const float d = ld_half(p), dmin = ld_half(p + 2);
+        uint32_t sc, mn;
+        scale_min(p + 4, e >> 5, sc, mn);
+        const uint8_t* qs = p + (QT == Q4_K ? 16 : 48);
+        int q = (__ldg(qs + (e >> 6) * 32 + (e & 31)) >> (4 * ((e >> 5) & 1))) & 0xF;
+        if constexpr (QT == Q5_K) q |= ((__ldg(p + 16 + (e & 31)) >> (e >> 5)) & 1) << 4;
+        float v = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
+        return to_field(v, S);
+    }
+}
+
+__device__ __forceinline__ uint64_t lift_any(int qtype, const uint8_t* __restrict__ raw, int64_t widx, double S) {
+    const uint8_t* p = raw + (widx >> 8) * block_bytes(qtype);
+    const int e = (int)(widx & 255);
+    return qtype == Q4_K ? lift<Q4_K>(p, e, S) : qtype == Q5_K ? lift<Q5_K>(p, e, S) : lift<Q6_K>(p, e, S);
+}
+
+}  // namespace vkq

@@ -1,0 +1,675 @@
+// Goldilocks NTT and fused Reed-Solomon row encode for sm_100a.
+//
+// What it replaces in the reference: the batched NTT engine
+// (prover/kernels/ntt.cuh:310-770, prover/cuda_primitives.py:347-409) and the
+// encode pipeline built on it (prover/core.py:721-802, layergkr/gpu.py:141-203).
+//
+// Design (differs from the reference's bit-reverse + per-stage passes):
+//  * A transform of length n is n = n1*n2 (four-step); each step is a *tile pass*:
+//    a CTA owns a tile of C columns x L points, keeps it in shared memory and runs
+//    a Stockham autosort DFT of length L with radix-16 register butterflies.
+//  * Inside a radix-16 butterfly every twiddle is a power of two (w_16 = 2^156 in
+//    this field), so the register stages use shifts only; one full 64x64->128
+//    modular multiply per element per shared-memory stage remains.
+//  * Natural order in, natural order out; no bit-reversal pass, no scale pass
+//    (n^-1 is folded into the last stage), intermediates of a row chunk stay in a
+//    caller-provided scratch buffer sized to remain L2-resident.
+//  * The encode runs three passes per row chunk: iNTT step 1 (message + pad
+//    loader), iNTT step 2 fused with the coset twist and step 1 of all rho coset
+//    NTTs, and step 2 of the coset NTTs writing the interleaved codeword.
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "../../include/verinf_b200.h"
+#include "blake3.cuh"
+#include "common.cuh"
+#include "gl.cuh"
+#include "kquant.cuh"
+
+namespace {
+
+using vgl::add;
+using vgl::mul;
+using vgl::sub;
+
+// w_R = 2^root_exp(log2 R): the reference's root_of_unity(R) = 7^((p-1)/R) for R = 2..64.
+__host__ __device__ constexpr int root_exp(int logr) {
+    return logr == 1 ? 96 : logr == 2 ? 48 : logr == 3 ? 120 : logr == 4 ? 156 : logr == 5 ? 78 : 39;
+}
+
+template <int LOGLEN, int K, bool INV>
+__device__ __forceinline__ void bfly(uint64_t& a, uint64_t& b) {
+    constexpr int s0 = (root_exp(LOGLEN) * K) % 192;
+    constexpr int s = INV ? (192 - s0) % 192 : s0;
+    uint64_t t = add(a, b);
+    uint64_t d = (s >= 96) ? sub(b, a) : sub(a, b);   // 2^96 = -1
+    a = t;
+    b = vgl::mul_pow2<s % 96>(d);
+}
+
+template <int LOGR, int LOGLEN, int I, bool INV>
+__device__ __forceinline__ void dif_level(uint64_t* v) {
+    constexpr int R = 1 << LOGR, LEN = 1 << LOGLEN, HALF = LEN / 2;
+    if constexpr (I < R / 2) {
+        constexpr int blk = I / HALF, k = I % HALF;
+        bfly<LOGLEN, k, INV>(v[blk * LEN + k], v[blk * LEN + k + HALF]);
+        dif_level<LOGR, LOGLEN, I + 1, INV>(v);
+    }
+}
+// In-register decimation-in-frequency DFT of R = 2^LOGR values: X[c] = v[bitrev(c)].
+template <int LOGR, int LOGLEN, bool INV>
+__device__ __forceinline__ void dif(uint64_t* v) {
+    if constexpr (LOGLEN >= 1) {
+        dif_level<LOGR, LOGLEN, 0, INV>(v);
+        dif<LOGR, LOGLEN - 1, INV>(v);
+    }
+}
+
+__host__ __device__ constexpr int brev(int x, int bits) {
+    int r = 0;
+    for (int i = 0; i < bits; ++i) r |= ((x >> i) & 1) << (bits - 1 - i);
+    return r;
+}
+
+// Stage schedule of a length-2^LOGL tile DFT: radix-16 stages plus one smaller
+// stage (first or last).  A thread owns EPT elements of one column.
+template <int LOGL, bool SMALL_LAST>
+struct Sched {
+    static constexpr int B = LOGL % 4;
+    static constexpr int NS = LOGL == 0 ? 0 : (LOGL < 4 ? 1 : LOGL / 4 + (B ? 1 : 0));
+    static constexpr int EPT = LOGL >= 4 ? 16 : (1 << LOGL);
+    static constexpr int TPC = (1 << LOGL) / EPT;   // threads per column
+    __host__ __device__ static constexpr int logr(int s) {
+        if (LOGL < 4) return LOGL;
+        if (B == 0) return 4;
+        if (SMALL_LAST) return s == NS - 1 ? B : 4;
+        return s == 0 ? B : 4;
+    }
+    __host__ __device__ static constexpr int logp(int s) {
+        int p = 0;
+        for (int i = 0; i < s; ++i) p += logr(i);
+        return p;
+    }
+    // register j of the first stage holds input index first_pos(j, w)
+    __host__ __device__ static constexpr int first_pos(int j, int w) {
+        if (NS == 0) return 0;
+        int r = 1 << logr(0);
+        return (w + (j / r) * TPC) + (j % r) * ((1 << LOGL) / r);
+    }
+    // register j after the last stage holds output index last_k(j, w)
+    __host__ __device__ static constexpr int last_k(int j, int w) {
+        if (NS == 0) return 0;
+        int lr = logr(NS - 1), r = 1 << lr;
+        return (w + (j / r) * TPC) + brev(j % r, lr) * ((1 << LOGL) / r);
+    }
+};
+
+template <bool INV>
+__device__ __forceinline__ uint64_t tw_at(const uint64_t* __restrict__ tw, uint32_t e, uint32_t mask) {
+    return INV ? __ldg(tw + ((0u - e) & mask)) : __ldg(tw + e);   // w^-e = w^(n-e)
+}
+
+// Stages S..NS-1 of the tile DFT.  v is preloaded for stage S; on return it holds
+// the outputs of the last stage (see Sched::last_k).  sm is the tile [pos*CP + col].
+template <int LOGL, bool INV, bool SMALL_LAST, int S>
+__device__ __forceinline__ void run_stages(uint64_t (&v)[Sched<LOGL, SMALL_LAST>::EPT], uint64_t* sm,
+                                           int CP, int col, int w, const uint64_t* __restrict__ twL) {
+    using SC = Sched<LOGL, SMALL_LAST>;
+    if constexpr (S < SC::NS) {
+        constexpr int LOGR = SC::logr(S), R = 1 << LOGR, G = SC::EPT / R, LOGP = SC::logp(S);
+        constexpr int L = 1 << LOGL, PP = 1 << LOGP;
+        constexpr bool LAST = (S == SC::NS - 1);
+        if constexpr (S > 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int i = 0; i < R; ++i)
+                    v[g * R + i] = sm[((w + g * SC::TPC) + i * (L / R)) * CP + col];
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) dif<LOGR, LOGR, INV>(&v[g * R]);
+        if constexpr (!LAST) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                uint32_t qp = (uint32_t)(w + g * SC::TPC) >> LOGP;
+#pragma unroll
+                for (int c = 1; c < R; ++c) {
+                    uint32_t e = (qp * c) << LOGP;
+                    v[g * R + brev(c, LOGR)] = mul(v[g * R + brev(c, LOGR)], tw_at<INV>(twL, e, L - 1));
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                int x = w + g * SC::TPC;
+                int kappa = x & (PP - 1), qp = x >> LOGP;
+#pragma unroll
+                for (int c = 0; c < R; ++c)
+                    sm[(qp * PP * R + kappa + PP * c) * CP + col] = v[g * R + brev(c, LOGR)];
+            }
+            __syncthreads();
+            run_stages<LOGL, INV, SMALL_LAST, S + 1>(v, sm, CP, col, w, twL);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Generic tile pass.
+// ---------------------------------------------------------------------------
+enum { SRC_PLAIN = 0, SRC_MSG = 1, SRC_KQ = 2 };
+
+struct PassArgs {
+    const uint64_t* in;
+    uint64_t* out;
+    int logC;
+    int64_t ncols;           // columns per item
+    int64_t tiles_per_item;
+    int64_t in_item, in_idx, in_col;
+    int64_t out_item, out_k, out_col;
+    const uint64_t* twL;     // w_L^e, e < L
+    const uint64_t* twN;     // w_n^e, e < n (four-step factor w_n^(col*k)) or null
+    uint32_t twN_mask;
+    uint64_t scale;          // multiply outputs by this unless 1
+    int out_via_smem;        // outputs are contiguous along k: transpose through smem
+    // SRC_MSG loader: input element (item=row, pos, col) is slot j = pos*in_idx + col of the
+    // padded message row: j < ell -> msg[row*ell + j]; else zero or the pad PRG.
+    int src_kind;
+    int64_t ell;
+    int pad_mode;            // 0 zeros, 1 PRG
+    const uint8_t* seed;     // device pointer, 32 bytes (pad_mode 1)
+    int64_t row_off;
+    // SRC_KQ loader: slot j < ell of row `item` is element f = (kq_first_row + item)*ell + j of the
+    // lifted (d_out, d_in) K-quant matrix (transposed view when kq_transpose), zero past its end.
+    const uint8_t* kq_raw;
+    int kq_type;
+    int kq_transpose;
+    double kq_S;
+    int64_t kq_dout, kq_din, kq_first_row;
+};
+
+template <int LOGL, bool INV, int MODE>   // MODE 0: input contiguous along columns; 1: along the DFT index
+__global__ void __launch_bounds__(512) k_pass(PassArgs a) {
+    using SC = Sched<LOGL, false>;
+    constexpr int L = 1 << LOGL, EPT = SC::EPT;
+    extern __shared__ uint64_t sm[];
+    const int tid = threadIdx.x, C = 1 << a.logC, CP = C + 1;
+    const int col = tid & (C - 1), w = tid >> a.logC;
+    const int64_t item = blockIdx.x / a.tiles_per_item;
+    const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
+    const int64_t colg = col0 + col;
+    const bool valid = colg < a.ncols;
+    uint64_t v[EPT];
+
+    if constexpr (MODE == 0) {
+        if (a.src_kind == SRC_PLAIN) {
+            const uint64_t* src = a.in + item * a.in_item + colg * a.in_col;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                v[j] = valid ? src[(int64_t)SC::first_pos(j, w) * a.in_idx] : 0;
+        } else {
+            const uint64_t* src = a.in + item * a.ell;
+            uint32_t seed[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (a.pad_mode == 1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    seed[i] = (uint32_t)__ldg(a.seed + 4 * i) | ((uint32_t)__ldg(a.seed + 4 * i + 1) << 8) |
+                              ((uint32_t)__ldg(a.seed + 4 * i + 2) << 16) | ((uint32_t)__ldg(a.seed + 4 * i + 3) << 24);
+            }
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                int64_t slot = (int64_t)SC::first_pos(j, w) * a.in_idx + colg;
+                uint64_t x = 0;
+                if (valid) {
+                    if (slot < a.ell) {
+                        if (a.src_kind == SRC_MSG) x = src[slot];
+                        else {
+                            int64_t f = (a.kq_first_row + item) * a.ell + slot;
+                            if (f < a.kq_dout * a.kq_din) {
+                                int64_t widx = a.kq_transpose ? (f % a.kq_dout) * a.kq_din + f / a.kq_dout : f;
+                                x = vkq::lift_any(a.kq_type, a.kq_raw, widx, a.kq_S);
+                            }
+                        }
+                    } else if (a.pad_mode == 1) x = vb3::pad_prg(seed, (uint64_t)(a.row_off + item), (uint64_t)(slot - a.ell));
+                }
+                v[j] = x;
+            }
+        }
+    } else {
+        const int nthr = blockDim.x;
+        const uint64_t* src = a.in + item * a.in_item;
+        for (int e = tid; e < L * C; e += nthr) {
+            int idx = e & (L - 1), cl = e >> LOGL;
+            int64_t cg = col0 + cl;
+            sm[idx * CP + cl] = cg < a.ncols ? src[cg * a.in_col + (int64_t)idx * a.in_idx] : 0;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) v[j] = sm[SC::first_pos(j, w) * CP + col];
+    }
+
+    run_stages<LOGL, INV, false, 0>(v, sm, CP, col, w, a.twL);
+
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        uint32_t k = SC::last_k(j, w);
+        if (a.twN) v[j] = mul(v[j], tw_at<INV>(a.twN, (uint32_t)colg * k, a.twN_mask));
+        if (a.scale != 1) v[j] = mul(v[j], a.scale);
+    }
+    if (!a.out_via_smem) {
+        if (valid) {
+            uint64_t* dst = a.out + item * a.out_item + colg * a.out_col;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) dst[(int64_t)SC::last_k(j, w) * a.out_k] = v[j];
+        }
+    } else {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) sm[SC::last_k(j, w) * CP + col] = v[j];
+        __syncthreads();
+        const int nthr = blockDim.x;
+        uint64_t* dst = a.out + item * a.out_item;
+        for (int e = tid; e < L * C; e += nthr) {
+            int k = e & (L - 1), cl = e >> LOGL;
+            int64_t cg = col0 + cl;
+            if (cg < a.ncols) dst[cg * a.out_col + (int64_t)k * a.out_k] = sm[k * CP + cl];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Encode middle pass: iNTT step 2 -> coefficients (x K^-1) -> for each coset t:
+// twist by (7*w_N^t)^l, NTT step 1, four-step factor, store for step 2.
+// Coefficients stay in registers across the rho cosets.
+// ---------------------------------------------------------------------------
+struct MidArgs {
+    const uint64_t* s1;    // (rows, K): [k1*L + j2]
+    uint64_t* polys;       // (rows, K) natural order, or null
+    uint64_t* s2;          // (rows, rho*K): [(m1*rho + t)*n1 + l2], or null
+    int logC;
+    int64_t n1;            // number of columns (= K / L)
+    int64_t tiles_per_item;
+    int rho;
+    int64_t K;
+    const uint64_t* twL;   // w_L^e
+    const uint64_t* twK;   // w_K^e
+    const uint64_t* twist; // (rho, K): (7*w_N^t)^l
+    uint64_t k_inv;
+};
+
+template <int LOGL>
+__global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
+    using SI = Sched<LOGL, false>;   // inverse: small stage first, radix-16 last
+    using SF = Sched<LOGL, true>;    // forward: radix-16 first, small stage last
+    constexpr int L = 1 << LOGL, EPT = SI::EPT;
+    constexpr int LR = SI::NS ? SI::logr(SI::NS - 1) : 0;   // last inverse radix == first forward radix
+    extern __shared__ uint64_t sm[];
+    const int tid = threadIdx.x, C = 1 << a.logC, CP = C + 1;
+    const int col = tid & (C - 1), w = tid >> a.logC;
+    const int64_t item = blockIdx.x / a.tiles_per_item;
+    const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
+    const int64_t colg = col0 + col;
+    const bool valid = colg < a.n1;
+
+    {
+        const int nthr = blockDim.x;
+        const uint64_t* src = a.s1 + item * a.K;
+        for (int e = tid; e < L * C; e += nthr) {
+            int idx = e & (L - 1), cl = e >> LOGL;
+            int64_t cg = col0 + cl;
+            sm[idx * CP + cl] = cg < a.n1 ? src[cg * L + idx] : 0;
+        }
+        __syncthreads();
+    }
+    uint64_t c[EPT], v[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) c[j] = sm[SI::first_pos(j, w) * CP + col];
+    run_stages<LOGL, true, false, 0>(c, sm, CP, col, w, a.twL);
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) c[j] = mul(c[j], a.k_inv);
+    if (a.polys && valid) {
+        uint64_t* dst = a.polys + item * a.K + colg;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) dst[(int64_t)SI::last_k(j, w) * a.n1] = c[j];
+    }
+    if (!a.s2) return;
+    uint64_t* dst2 = a.s2 + item * a.K * a.rho + colg;
+    for (int t = 0; t < a.rho; ++t) {
+        const uint64_t* tw_t = a.twist + (int64_t)t * a.K;
+        if (SF::NS > 1) __syncthreads();   // previous coset finished reading the tile
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            // forward register j needs coefficient index l1 = first_pos(j): it is held in c[brev(j)]
+            int l1 = SF::first_pos(j, w);
+            int64_t l = colg + a.n1 * (int64_t)l1;
+            uint64_t tw = valid ? __ldg(tw_t + l) : 0;
+            v[j] = mul(c[(j / (1 << LR)) * (1 << LR) + brev(j % (1 << LR), LR)], tw);
+        }
+        run_stages<LOGL, false, true, 0>(v, sm, CP, col, w, a.twL);
+        if (valid) {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                uint32_t m1 = SF::last_k(j, w);
+                uint64_t x = mul(v[j], __ldg(a.twK + (uint32_t)colg * m1));
+                dst2[((int64_t)m1 * a.rho + t) * a.n1] = x;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: twiddle cache, launch planning.
+// ---------------------------------------------------------------------------
+struct DevTables {
+    std::map<int64_t, uint64_t*> tw;                          // n -> w_n^e, e < n
+    std::map<std::pair<int64_t, int64_t>, uint64_t*> twist;   // (K, N) -> (rho, K)
+};
+std::mutex g_mu;
+std::map<int, DevTables> g_tables;
+
+int get_tw(int64_t n, const uint64_t** out) {
+    int dev;
+    VI_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto& T = g_tables[dev];
+    auto it = T.tw.find(n);
+    if (it != T.tw.end()) { *out = it->second; return VI_OK; }
+    std::vector<uint64_t> h((size_t)n);
+    uint64_t wn = vgl::hpow(7, (vgl::P - 1) / (uint64_t)n), cur = 1;
+    for (int64_t e = 0; e < n; ++e) { h[(size_t)e] = cur; cur = vgl::hmul(cur, wn); }
+    uint64_t* d = nullptr;
+    VI_CUDA(cudaMalloc(&d, (size_t)n * 8));
+    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
+    T.tw[n] = d;
+    *out = d;
+    return VI_OK;
+}
+
+int get_twist(int64_t K, int64_t N, const uint64_t** out) {
+    int dev;
+    VI_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto& T = g_tables[dev];
+    auto key = std::make_pair(K, N);
+    auto it = T.twist.find(key);
+    if (it != T.twist.end()) { *out = it->second; return VI_OK; }
+    int64_t rho = N / K;
+    std::vector<uint64_t> h((size_t)(rho * K));
+    uint64_t wN = vgl::hpow(7, (vgl::P - 1) / (uint64_t)N);
+    for (int64_t t = 0; t < rho; ++t) {
+        uint64_t g = vgl::hmul(7, vgl::hpow(wN, (uint64_t)t)), cur = 1;
+        for (int64_t l = 0; l < K; ++l) { h[(size_t)(t * K + l)] = cur; cur = vgl::hmul(cur, g); }
+    }
+    uint64_t* d = nullptr;
+    VI_CUDA(cudaMalloc(&d, (size_t)(rho * K) * 8));
+    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)(rho * K) * 8, cudaMemcpyHostToDevice));
+    T.twist[key] = d;
+    *out = d;
+    return VI_OK;
+}
+
+constexpr int MAX_LOGL = 10;
+
+// columns per tile for a DFT length 2^logL given ncols available
+int pick_logC(int logL, int64_t ncols) {
+    int logC = logL <= 8 ? 12 - logL : 13 - logL;      // 4096-element tiles, 8192 for long DFTs
+    int logTPC = logL >= 4 ? logL - 4 : 0;
+    if (logC > 9 - logTPC) logC = 9 - logTPC;          // at most 512 threads
+    int need = vi::ilog2(ncols);
+    if (need < 4) need = 4;
+    if (logC > need) logC = need;
+    if (logC < 3) logC = 3;
+    return logC;
+}
+int tile_threads(int logL, int logC) {
+    int ept = logL >= 4 ? 16 : (1 << logL);
+    return ((1 << logL) / ept) << logC;
+}
+size_t tile_smem(int logL, int logC) { return (size_t)(1 << logL) * ((1 << logC) + 1) * 8; }
+
+template <int LOGL, bool INV, int MODE>
+int launch_pass_t(const PassArgs& a, int64_t items, cudaStream_t st) {
+    size_t smem = tile_smem(LOGL, a.logC);
+    auto fn = k_pass<LOGL, INV, MODE>;
+    if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid = items * a.tiles_per_item;
+    if (grid <= 0) return VI_OK;
+    if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "tile grid too large (%lld)", (long long)grid);
+    fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
+    return vi::check_launch("k_pass");
+}
+
+template <bool INV, int MODE>
+int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st) {
+    switch (logL) {
+#define VI_CASE(x) case x: return launch_pass_t<x, INV, MODE>(a, items, st);
+        VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
+        VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
+#undef VI_CASE
+    }
+    return vi::fail(VI_ERR_LIMIT, "unsupported tile length 2^%d", logL);
+}
+
+int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaStream_t st) {
+    a.tiles_per_item = (a.ncols + (1 << a.logC) - 1) >> a.logC;
+    int rc = get_tw(int64_t(1) << logL, &a.twL);
+    if (rc) return rc;
+    if (inv) return mode ? launch_pass_l<true, 1>(logL, a, items, st) : launch_pass_l<true, 0>(logL, a, items, st);
+    return mode ? launch_pass_l<false, 1>(logL, a, items, st) : launch_pass_l<false, 0>(logL, a, items, st);
+}
+
+template <int LOGL>
+int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
+    size_t smem = tile_smem(LOGL, a.logC);
+    auto fn = k_encode_mid<LOGL>;
+    if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid = items * a.tiles_per_item;
+    if (grid <= 0) return VI_OK;
+    if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "tile grid too large (%lld)", (long long)grid);
+    fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
+    return vi::check_launch("k_encode_mid");
+}
+int launch_mid(int logL, const MidArgs& a, int64_t items, cudaStream_t st) {
+    switch (logL) {
+#define VI_CASE(x) case x: return launch_mid_t<x>(a, items, st);
+        VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
+        VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
+#undef VI_CASE
+    }
+    return vi::fail(VI_ERR_LIMIT, "unsupported tile length 2^%d", logL);
+}
+
+uint64_t inv_pow2(int log) {   // 2^-log mod p
+    return vgl::hpow(vgl::hpow(2, (uint64_t)log), vgl::P - 2);
+}
+
+constexpr int64_t L2_CHUNK_BYTES = 40ll << 20;   // keep a chunk's intermediates L2-resident
+
+}  // namespace
+
+namespace vi {
+static thread_local char g_err[512] = "";
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(VI_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
+    return VI_OK;
+}
+}  // namespace vi
+
+extern "C" const char* vi_last_error(void) { return vi::g_err; }
+
+extern "C" int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n) {
+    if (n <= (int64_t(1) << MAX_LOGL) || m <= 0) return 0;
+    int64_t row = n * 8;
+    int64_t rows = L2_CHUNK_BYTES / row;
+    if (rows < 1) rows = 1;
+    if (rows > m) rows = m;
+    return rows * row;
+}
+
+extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
+                              void* scratch, int64_t scratch_bytes, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    VI_REQUIRE(m >= 0, "ntt: negative row count");
+    VI_REQUIRE(vi::is_pow2(n) && n >= 2, "NTT length must be a power of 2 >= 2 (got %lld)", (long long)n);
+    int logn = vi::ilog2(n);
+    if (logn > 2 * MAX_LOGL) return vi::fail(VI_ERR_LIMIT, "NTT length 2^%d exceeds the supported 2^%d", logn, 2 * MAX_LOGL);
+    if (m == 0) return VI_OK;
+    VI_REQUIRE(rows != nullptr, "ntt: null data pointer");
+    const bool inv = inverse != 0;
+    const uint64_t scale = inv ? inv_pow2(logn) : 1;
+    if (logn <= MAX_LOGL) {
+        PassArgs a{};
+        a.in = rows; a.out = rows;
+        a.logC = pick_logC(logn, m);
+        a.ncols = m;
+        a.in_item = 0; a.in_idx = 1; a.in_col = n;
+        a.out_item = 0; a.out_k = 1; a.out_col = n;
+        a.twN = nullptr; a.scale = scale; a.out_via_smem = 1; a.src_kind = SRC_PLAIN;
+        return launch_pass(logn, inv, 1, a, 1, st);
+    }
+    const int log1 = (logn + 1) / 2, log2 = logn - log1;
+    const int64_t n1 = int64_t(1) << log1, n2 = int64_t(1) << log2;
+    VI_REQUIRE(scratch != nullptr && scratch_bytes >= n * 8,
+               "ntt: scratch of at least %lld bytes required (see vi_ntt_scratch_bytes)", (long long)(n * 8));
+    int64_t chunk = scratch_bytes / (n * 8);
+    const uint64_t* twn;
+    int rc = get_tw(n, &twn);
+    if (rc) return rc;
+    for (int64_t r0 = 0; r0 < m; r0 += chunk) {
+        int64_t cnt = m - r0 < chunk ? m - r0 : chunk;
+        PassArgs a{};
+        a.in = rows + r0 * n; a.out = (uint64_t*)scratch;
+        a.logC = pick_logC(log1, n2);
+        a.ncols = n2;
+        a.in_item = n; a.in_idx = n2; a.in_col = 1;
+        a.out_item = n; a.out_k = n2; a.out_col = 1;
+        a.twN = twn; a.twN_mask = (uint32_t)(n - 1); a.scale = 1; a.out_via_smem = 0; a.src_kind = SRC_PLAIN;
+        rc = launch_pass(log1, inv, 0, a, cnt, st);
+        if (rc) return rc;
+        PassArgs b{};
+        b.in = (const uint64_t*)scratch; b.out = rows + r0 * n;
+        b.logC = pick_logC(log2, n1);
+        b.ncols = n1;
+        b.in_item = n; b.in_idx = 1; b.in_col = n2;
+        b.out_item = n; b.out_k = n1; b.out_col = 1;
+        b.twN = nullptr; b.scale = scale; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
+        rc = launch_pass(log2, inv, 1, b, cnt, st);
+        if (rc) return rc;
+    }
+    return VI_OK;
+}
+
+extern "C" int64_t vi_encode_scratch_bytes(int64_t m, int64_t k, int64_t n) {
+    if (m <= 0) return 0;
+    int64_t row = (k + n) * 8;
+    int64_t rows = L2_CHUNK_BYTES / row;
+    if (rows < 1) rows = 1;
+    if (rows > m) rows = m;
+    return rows * row;
+}
+
+namespace {
+struct KqSrc { const uint8_t* raw; int qtype; int transpose; double S; int64_t d_out, d_in, first_row; };
+}
+
+static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t ell, int64_t k, int64_t n,
+                       int pad_mode, const uint8_t* seed_dev32, int64_t row_off,
+                       uint64_t* polys, uint64_t* codes,
+                       void* scratch, int64_t scratch_bytes, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    VI_REQUIRE(m >= 0, "encode: negative row count");
+    VI_REQUIRE(vi::is_pow2(k) && k >= 2, "encode: K must be a power of 2 >= 2 (got %lld)", (long long)k);
+    VI_REQUIRE(vi::is_pow2(n) && n >= k, "encode: N must be a power of 2 >= K (got %lld)", (long long)n);
+    VI_REQUIRE(ell >= 0 && ell <= k, "encode: need 0 <= ELL <= K");
+    VI_REQUIRE(pad_mode == 0 || pad_mode == 1, "encode: pad_mode must be 0 (zeros) or 1 (PRG)");
+    VI_REQUIRE(pad_mode == 0 || ell == k || seed_dev32 != nullptr, "encode: PRG pad needs a 32-byte seed");
+    const int logk = vi::ilog2(k);
+    if (logk > 2 * MAX_LOGL) return vi::fail(VI_ERR_LIMIT, "encode: K = 2^%d exceeds the supported 2^%d", logk, 2 * MAX_LOGL);
+    const int64_t rho = n / k;
+    VI_REQUIRE(rho * k < (int64_t(1) << 31), "encode: N too large");
+    if (m == 0) return VI_OK;
+    VI_REQUIRE(kq != nullptr || msg != nullptr || ell == 0, "encode: null message pointer");
+    const int log1 = (logk + 1) / 2, log2 = logk - log1;
+    const int64_t n1 = int64_t(1) << log1, n2 = int64_t(1) << log2;
+    const int64_t per_row = (k + (codes ? n : 0)) * 8;
+    VI_REQUIRE(scratch != nullptr && scratch_bytes >= per_row,
+               "encode: scratch of at least %lld bytes required (see vi_encode_scratch_bytes)", (long long)per_row);
+    int64_t chunk = scratch_bytes / per_row;
+    const uint64_t *twk, *twist = nullptr;
+    int rc = get_tw(k, &twk);
+    if (rc) return rc;
+    if (codes) { rc = get_twist(k, n, &twist); if (rc) return rc; }
+    uint64_t* s1 = (uint64_t*)scratch;
+    for (int64_t r0 = 0; r0 < m; r0 += chunk) {
+        int64_t cnt = m - r0 < chunk ? m - r0 : chunk;
+        uint64_t* s2 = s1 + cnt * k;
+        // pass 1: inverse step 1 over j1 (length n1) for column tiles of j2
+        PassArgs a{};
+        a.in = kq ? nullptr : msg + r0 * ell; a.out = s1;
+        a.logC = pick_logC(log1, n2);
+        a.ncols = n2;
+        a.in_item = ell; a.in_idx = n2; a.in_col = 1;
+        a.out_item = k; a.out_k = n2; a.out_col = 1;
+        a.twN = twk; a.twN_mask = (uint32_t)(k - 1); a.scale = 1; a.out_via_smem = 0;
+        a.src_kind = kq ? SRC_KQ : SRC_MSG; a.ell = ell;
+        if (kq) {
+            a.kq_raw = kq->raw; a.kq_type = kq->qtype; a.kq_transpose = kq->transpose; a.kq_S = kq->S;
+            a.kq_dout = kq->d_out; a.kq_din = kq->d_in; a.kq_first_row = kq->first_row + r0;
+        } a.pad_mode = (ell < k) ? pad_mode : 0; a.row_off = row_off + r0;
+        a.seed = seed_dev32;
+        rc = launch_pass(log1, true, 0, a, cnt, st);
+        if (rc) return rc;
+        // pass 2: inverse step 2 (length n2) + twist + forward step 1 for every coset
+        MidArgs mid{};
+        mid.s1 = s1; mid.polys = polys ? polys + r0 * k : nullptr; mid.s2 = codes ? s2 : nullptr;
+        mid.logC = pick_logC(log2, n1);
+        mid.n1 = n1; mid.tiles_per_item = (n1 + (1 << mid.logC) - 1) >> mid.logC;
+        mid.rho = (int)rho; mid.K = k; mid.twK = twk; mid.twist = twist; mid.k_inv = inv_pow2(logk);
+        rc = get_tw(n2, &mid.twL);
+        if (rc) return rc;
+        rc = launch_mid(log2, mid, cnt, st);
+        if (rc) return rc;
+        if (!codes) continue;
+        // pass 3: forward step 2 (length n1) for columns (m1, t), interleaved codeword out
+        PassArgs b{};
+        b.in = s2; b.out = codes + r0 * n;
+        b.ncols = rho * n2;
+        b.logC = pick_logC(log1, b.ncols);
+        b.in_item = n; b.in_idx = 1; b.in_col = n1;
+        b.out_item = n; b.out_k = rho * n2; b.out_col = 1;
+        b.twN = nullptr; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
+        rc = launch_pass(log1, false, 1, b, cnt, st);
+        if (rc) return rc;
+    }
+    return VI_OK;
+}
+
+extern "C" int vi_encode_rows(const uint64_t* msg, int64_t m, int64_t ell, int64_t k, int64_t n,
+                              int pad_mode, const uint8_t* seed_dev32, int64_t row_off,
+                              uint64_t* polys, uint64_t* codes,
+                              void* scratch, int64_t scratch_bytes, void* stream) {
+    return encode_impl(msg, nullptr, m, ell, k, n, pad_mode, seed_dev32, row_off, polys, codes,
+                       scratch, scratch_bytes, stream);
+}
+
+extern "C" int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, int64_t d_out, int64_t d_in,
+                                     int transpose, int64_t first_row, int64_t m,
+                                     int64_t ell, int64_t k, int64_t n,
+                                     int pad_mode, const uint8_t* seed_dev32, int64_t row_off,
+                                     uint64_t* polys, uint64_t* codes,
+                                     void* scratch, int64_t scratch_bytes, void* stream) {
+    VI_REQUIRE(qtype == 4 || qtype == 5 || qtype == 6, "kquant encode: qtype must be 4, 5 or 6");
+    VI_REQUIRE(d_out > 0 && d_in > 0 && (d_out * d_in) % 256 == 0, "kquant encode: d_out*d_in must be a multiple of 256");
+    VI_REQUIRE(first_row >= 0 && raw != nullptr, "kquant encode: bad source");
+    KqSrc kq{raw, qtype, transpose != 0, S, d_out, d_in, first_row};
+    return encode_impl(nullptr, &kq, m, ell, k, n, pad_mode, seed_dev32, row_off, polys, codes,
+                       scratch, scratch_bytes, stream);
+}

@@ -1,0 +1,253 @@
+// Sumcheck round kernel: fold with the previous challenge and evaluate the next
+// round polynomial in one pass over the tables.
+//
+// Replaces the per-round work of layergkr/gpu.py:326-410 (fold_t, gl_sum,
+// prove_terms_gpu; CPU twin layergkr/sumcheck.py:153-226), which issues ~10
+// elementwise launches and a host sync per sample point.  Here one launch reads each
+// table once, writes the folded half once and produces all deg+1 samples; a second
+// tiny launch adds the per-CTA partial sums.  The arithmetic per sample is the
+// reference's: g(x) = sum_i sum_t c_t prod_j (f[i] + x (f[half+i] - f[i])), variable
+// order most-significant first, so results are bit-identical (field sums commute).
+#include "../../include/verinf_b200.h"
+#include "common.cuh"
+#include "gl.cuh"
+
+namespace {
+
+using vgl::add;
+using vgl::mul;
+using vgl::sub;
+
+constexpr int MAX_TABLES = 8, MAX_TERMS = 8, MAX_FAC = 4, MAX_SAMPLES = 8;
+constexpr int BLOCK = 256;
+constexpr int MAX_GRID = 148 * 8;
+
+struct Problem {
+    uint64_t* tab[MAX_TABLES];
+    int n_tables, n_terms, deg;
+    uint64_t coef[MAX_TERMS];
+    int nfac[MAX_TERMS];
+    int fac[MAX_TERMS][MAX_FAC];
+    int simple;   // one term, coefficient 1, factors = tables 0..n_tables-1 in order
+};
+
+// Block-level sum of ns per-thread accumulators -> partials[block*MAX_SAMPLES + x]
+__device__ __forceinline__ void block_reduce(uint64_t (&acc)[MAX_SAMPLES], int ns, uint64_t* partials) {
+    __shared__ uint64_t red[BLOCK / 32][MAX_SAMPLES];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) {
+        if (x < ns) {
+            uint64_t v = acc[x];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v = add(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (lane == 0) red[wid][x] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < ns) {
+        uint64_t v = 0;
+#pragma unroll
+        for (int w = 0; w < BLOCK / 32; ++w) v = add(v, red[w][threadIdx.x]);
+        partials[(int64_t)blockIdx.x * MAX_SAMPLES + threadIdx.x] = v;
+    }
+}
+
+// MODE 0: claim (sum of products at every index, one "sample")
+// MODE 1: round samples on the tables as they are (pairs i, i+half)
+// MODE 2: fold with r (size -> size/2, in place), then round samples of the folded tables
+template <int MODE>
+__global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, uint64_t r, uint64_t* partials) {
+    __shared__ uint64_t slo[MAX_TABLES][BLOCK], sd[MAX_TABLES][BLOCK];
+    const int ns = MODE == 0 ? 1 : pb.deg + 1;
+    // number of work items: claim = size; plain round = size/2 pairs; fold+round = size/4 pairs of pairs
+    const int64_t items = MODE == 0 ? size : MODE == 1 ? size / 2 : size / 4;
+    const int64_t q = items;   // distance between the two entries of a pair (after folding in MODE 2)
+    uint64_t acc[MAX_SAMPLES];
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) acc[x] = 0;
+    const int tid = threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + tid; i < items; i += stride) {
+        // per table: lo = f(x=0), d = f(1) - f(0) of the (folded) pair
+#pragma unroll
+        for (int k = 0; k < MAX_TABLES; ++k) {
+            if (k < pb.n_tables) {
+                uint64_t* f = pb.tab[k];
+                uint64_t lo, hi;
+                if (MODE == 0) { lo = f[i]; hi = lo; }
+                else if (MODE == 1) { lo = f[i]; hi = f[i + q]; }
+                else {
+                    uint64_t a0 = f[i], b0 = f[i + q], a1 = f[i + 2 * q], b1 = f[i + 3 * q];
+                    lo = add(a0, mul(r, sub(a1, a0)));
+                    hi = add(b0, mul(r, sub(b1, b0)));
+                    f[i] = lo;
+                    f[i + q] = hi;
+                }
+                slo[k][tid] = lo;
+                sd[k][tid] = sub(hi, lo);
+            }
+        }
+        if (pb.simple) {
+            // product of all tables, evaluated at x = 0..deg by stepping each factor by d
+            uint64_t cur[MAX_FAC];
+#pragma unroll
+            for (int k = 0; k < MAX_FAC; ++k) cur[k] = k < pb.n_tables ? slo[k][tid] : 1;
+#pragma unroll
+            for (int x = 0; x < MAX_SAMPLES; ++x) {
+                if (x < ns) {
+                    uint64_t prod = cur[0];
+#pragma unroll
+                    for (int k = 1; k < MAX_FAC; ++k)
+                        if (k < pb.n_tables) prod = mul(prod, cur[k]);
+                    acc[x] = add(acc[x], prod);
+#pragma unroll
+                    for (int k = 0; k < MAX_FAC; ++k)
+                        if (k < pb.n_tables) cur[k] = add(cur[k], sd[k][tid]);
+                }
+            }
+        } else {
+            for (int t = 0; t < pb.n_terms; ++t) {
+                uint64_t cur[MAX_FAC], dd[MAX_FAC];
+#pragma unroll
+                for (int j = 0; j < MAX_FAC; ++j) {
+                    int k = j < pb.nfac[t] ? pb.fac[t][j] : 0;
+                    cur[j] = slo[k][tid];
+                    dd[j] = sd[k][tid];
+                }
+#pragma unroll
+                for (int x = 0; x < MAX_SAMPLES; ++x) {
+                    if (x < ns) {
+                        uint64_t prod = pb.coef[t];
+#pragma unroll
+                        for (int j = 0; j < MAX_FAC; ++j)
+                            if (j < pb.nfac[t]) prod = mul(prod, cur[j]);
+                        acc[x] = add(acc[x], prod);
+#pragma unroll
+                        for (int j = 0; j < MAX_FAC; ++j) cur[j] = add(cur[j], dd[j]);
+                    }
+                }
+            }
+        }
+    }
+    block_reduce(acc, ns, partials);
+}
+
+__global__ void __launch_bounds__(BLOCK) k_sumcheck_finish(const uint64_t* __restrict__ partials, int n_blocks,
+                                                           int ns, uint64_t* __restrict__ out) {
+    uint64_t acc[MAX_SAMPLES];
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) acc[x] = 0;
+    for (int b = threadIdx.x; b < n_blocks; b += BLOCK)
+#pragma unroll
+        for (int x = 0; x < MAX_SAMPLES; ++x)
+            if (x < ns) acc[x] = add(acc[x], partials[(int64_t)b * MAX_SAMPLES + x]);
+    __shared__ uint64_t red[BLOCK / 32][MAX_SAMPLES];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) {
+        if (x < ns) {
+            uint64_t v = acc[x];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v = add(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (lane == 0) red[wid][x] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < ns) {
+        uint64_t v = 0;
+#pragma unroll
+        for (int w = 0; w < BLOCK / 32; ++w) v = add(v, red[w][threadIdx.x]);
+        out[threadIdx.x] = v;
+    }
+}
+
+// last fold: size 2 -> 1, no samples
+__global__ void k_final_fold(Problem pb, uint64_t r) {
+    int k = threadIdx.x;
+    if (k < pb.n_tables) {
+        uint64_t* f = pb.tab[k];
+        f[0] = add(f[0], mul(r, sub(f[1], f[0])));
+    }
+}
+
+int make_problem(Problem& pb, uint64_t* tables, int64_t stride, int n_tables, int n_terms,
+                 const uint64_t* coefs, const int32_t* nfac, const int32_t* fac) {
+    VI_REQUIRE(n_tables >= 1 && n_tables <= MAX_TABLES, "sumcheck: 1..%d tables supported (got %d)", MAX_TABLES, n_tables);
+    VI_REQUIRE(n_terms >= 1 && n_terms <= MAX_TERMS, "sumcheck: 1..%d terms supported (got %d)", MAX_TERMS, n_terms);
+    VI_REQUIRE(tables && coefs && nfac && fac, "sumcheck: null pointer");
+    pb.n_tables = n_tables; pb.n_terms = n_terms; pb.deg = 0;
+    for (int k = 0; k < MAX_TABLES; ++k) pb.tab[k] = k < n_tables ? tables + (int64_t)k * stride : nullptr;
+    for (int t = 0; t < MAX_TERMS; ++t) {
+        pb.coef[t] = 0; pb.nfac[t] = 0;
+        for (int j = 0; j < MAX_FAC; ++j) pb.fac[t][j] = 0;
+    }
+    for (int t = 0; t < n_terms; ++t) {
+        VI_REQUIRE(nfac[t] >= 1 && nfac[t] <= MAX_FAC, "sumcheck: a term needs 1..%d factors", MAX_FAC);
+        VI_REQUIRE(coefs[t] < vgl::P, "sumcheck: coefficient not canonical");
+        pb.coef[t] = coefs[t]; pb.nfac[t] = nfac[t];
+        if (nfac[t] > pb.deg) pb.deg = nfac[t];
+        for (int j = 0; j < nfac[t]; ++j) {
+            int k = fac[t * MAX_FAC + j];
+            VI_REQUIRE(k >= 0 && k < n_tables, "sumcheck: factor index out of range");
+            pb.fac[t][j] = k;
+        }
+    }
+    pb.simple = (n_terms == 1 && coefs[0] == 1 && nfac[0] == n_tables && n_tables <= MAX_FAC);
+    if (pb.simple)
+        for (int j = 0; j < n_tables; ++j)
+            if (fac[j] != j) pb.simple = 0;
+    return VI_OK;
+}
+
+int grid_for(int64_t items) {
+    int64_t g = (items + BLOCK - 1) / BLOCK;
+    if (g < 1) g = 1;
+    return (int)(g < MAX_GRID ? g : MAX_GRID);
+}
+
+}  // namespace
+
+extern "C" int64_t vi_sumcheck_scratch_bytes(void) { return (int64_t)MAX_GRID * MAX_SAMPLES * 8; }
+
+extern "C" int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_tables, int64_t size,
+                                 int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
+                                 uint64_t* out, void* partials, void* stream) {
+    Problem pb;
+    int rc = make_problem(pb, const_cast<uint64_t*>(tables), stride, n_tables, n_terms, coefs, nfac, fac);
+    if (rc) return rc;
+    VI_REQUIRE(vi::is_pow2(size), "sumcheck: table size must be a power of two");
+    VI_REQUIRE(out && partials, "sumcheck: null output/scratch");
+    cudaStream_t st = (cudaStream_t)stream;
+    int g = grid_for(size);
+    k_sumcheck<0><<<g, BLOCK, 0, st>>>(pb, size, 0, (uint64_t*)partials);
+    k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, 1, out);
+    return vi::check_launch("k_sumcheck<claim>");
+}
+
+extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
+                                 int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
+                                 int fold, uint64_t r, uint64_t* out, void* partials, void* stream) {
+    Problem pb;
+    int rc = make_problem(pb, tables, stride, n_tables, n_terms, coefs, nfac, fac);
+    if (rc) return rc;
+    VI_REQUIRE(vi::is_pow2(size) && size >= 2, "sumcheck: table size must be a power of two >= 2");
+    VI_REQUIRE(pb.deg + 1 <= MAX_SAMPLES, "sumcheck: degree too large");
+    VI_REQUIRE(r < vgl::P, "sumcheck: challenge not canonical");
+    VI_REQUIRE(out && partials, "sumcheck: null output/scratch");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!fold) {
+        int g = grid_for(size / 2);
+        k_sumcheck<1><<<g, BLOCK, 0, st>>>(pb, size, 0, (uint64_t*)partials);
+        k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
+        return vi::check_launch("k_sumcheck<round>");
+    }
+    if (size == 2) {
+        k_final_fold<<<1, 32, 0, st>>>(pb, r);
+        return vi::check_launch("k_final_fold");
+    }
+    int g = grid_for(size / 4);
+    k_sumcheck<2><<<g, BLOCK, 0, st>>>(pb, size, r, (uint64_t*)partials);
+    k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
+    return vi::check_launch("k_sumcheck<fold+round>");
+}

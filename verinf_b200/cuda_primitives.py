@@ -1,0 +1,652 @@
+"""Drop-in replacement for the reference's prover/cuda_primitives.py, backed by the
+hand-written sm_100a kernels in libverinf_b200.so.
+
+Same public names, argument order, return types and in-place/returning behaviour as
+the reference module (prover/cuda_primitives.py:1086-1440): everything operates on
+contiguous torch.uint64 CUDA tensors holding canonical Goldilocks values; `ntt_*`
+mutate their argument and return None; `gl_axpy` mutates y;
+`lookup_multiplicities_into` accumulates.  Errors surface as RuntimeError, like the
+reference's TORCH_CHECKs.  Outputs are allocated with torch; kernels run on torch's
+current stream.  There is no CPU path: without the CUDA library the import fails.
+
+Extensions beyond the reference surface (used by the fused commit path):
+`gl_mul_rowvec`, `encode_rows`, `commit_rows`.
+"""
+import torch
+
+from . import _lib
+from ._lib import LIB, check, ptr, scratch, stream_ptr
+
+P = (1 << 64) - (1 << 32) + 1
+GLOBAL_G = 7
+
+_U64 = torch.uint64
+
+
+def _chk_u64(t, name="tensor"):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be CUDA")
+    if t.dtype != _U64:
+        raise RuntimeError(f"{name} dtype must be uint64")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _chk_seed_label(seed, label):
+    if not (isinstance(seed, torch.Tensor) and seed.is_cuda and seed.dtype == torch.uint8 and seed.numel() == 32):
+        raise RuntimeError("seed must be a 32-byte CUDA uint8 tensor")
+    if not (isinstance(label, torch.Tensor) and label.is_cuda and label.dtype == torch.uint8 and label.numel() <= 8):
+        raise RuntimeError("label must be a CUDA uint8 tensor of <= 8 bytes")
+    return seed.contiguous(), label.contiguous()
+
+
+# ---- elementwise field ---------------------------------------------------------
+def _binary(op, a, b, what):
+    _chk_u64(a, "a"); _chk_u64(b, "b")
+    if a.shape != b.shape:
+        raise RuntimeError(f"{what}: shape mismatch")
+    out = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        check(LIB.vi_gl_binary(op, ptr(a), ptr(b), ptr(out), a.numel(), stream_ptr()))
+    return out
+
+
+def gl_mul(a, b): return _binary(0, a, b, "gl_mul")
+def gl_add(a, b): return _binary(1, a, b, "gl_add")
+def gl_sub(a, b): return _binary(2, a, b, "gl_sub")
+
+
+def gl_mul_rowvec(a, v):
+    """a (m, n) * v (n,) broadcast over rows, without materialising the broadcast."""
+    _chk_u64(a, "a"); _chk_u64(v, "v")
+    if a.numel() and (v.numel() == 0 or a.shape[-1] != v.numel()):
+        raise RuntimeError("gl_mul_rowvec: last dimension mismatch")
+    out = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        check(LIB.vi_gl_binary_bcast(0, ptr(a), ptr(v), max(v.numel(), 1), ptr(out), a.numel(), stream_ptr()))
+    return out
+
+
+def gl_neg(a):
+    _chk_u64(a, "a")
+    out = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        check(LIB.vi_gl_neg(ptr(a), ptr(out), a.numel(), stream_ptr()))
+    return out
+
+
+def gl_pow(base, exp):
+    _chk_u64(base, "base")
+    out = torch.empty_like(base)
+    with torch.cuda.device(base.device):
+        check(LIB.vi_gl_pow(ptr(base), int(exp) & ((1 << 64) - 1), ptr(out), base.numel(), stream_ptr()))
+    return out
+
+
+def gl_inv(a):
+    """Elementwise Fermat inverse a^(P-2)."""
+    return gl_pow(a, P - 2)
+
+
+def gl_inv_batched(a):
+    """Inverse of every element of a 1-D tensor (the unique inverse mod P)."""
+    _chk_u64(a, "a")
+    if a.dim() != 1:
+        raise RuntimeError("gl_inv_batched: 1-D input only")
+    return gl_pow(a, P - 2)
+
+
+def gl_axpy(y, alpha, x):
+    """In-place y += alpha * x mod P."""
+    _chk_u64(y, "y"); _chk_u64(x, "x")
+    if y.shape != x.shape:
+        raise RuntimeError("gl_axpy: shape mismatch")
+    with torch.cuda.device(y.device):
+        check(LIB.vi_gl_axpy(ptr(y), int(alpha) % P, ptr(x), y.numel(), stream_ptr()))
+
+
+# ---- NTT -------------------------------------------------------------------------
+def _ntt(rows, m, n, inverse):
+    if n < 2 or n & (n - 1):
+        raise RuntimeError("NTT length must be power of 2 >= 2")
+    with torch.cuda.device(rows.device):
+        nb = LIB.vi_ntt_scratch_bytes(m, n)
+        s = scratch(nb, rows.device) if nb else None
+        check(LIB.vi_ntt_batched(ptr(rows), m, n, int(inverse), ptr(s), nb, stream_ptr()))
+
+
+def ntt_forward(a):
+    _chk_u64(a, "a")
+    if a.dim() != 1:
+        raise RuntimeError("NTT input must be 1-D")
+    _ntt(a, 1, a.numel(), False)
+
+
+def ntt_inverse(a):
+    _chk_u64(a, "a")
+    if a.dim() != 1:
+        raise RuntimeError("NTT input must be 1-D")
+    _ntt(a, 1, a.numel(), True)
+
+
+def ntt_forward_batched(rows):
+    _chk_u64(rows, "rows")
+    if rows.dim() != 2:
+        raise RuntimeError("batched NTT expects (m, n)")
+    _ntt(rows, rows.size(0), rows.size(1), False)
+
+
+def ntt_inverse_batched(rows):
+    _chk_u64(rows, "rows")
+    if rows.dim() != 2:
+        raise RuntimeError("batched NTT expects (m, n)")
+    _ntt(rows, rows.size(0), rows.size(1), True)
+
+
+# ---- Reed-Solomon ------------------------------------------------------------------
+def rs_encode_rows(messages, n_lig, k_deg):
+    """(m, K_DEG) uint64 -> (m, N_LIG): iNTT_K of each row, zero-extended, NTT_N
+    (plain domain, no coset shift) — semantics of prover/cuda_primitives.py:417-456."""
+    _chk_u64(messages, "messages")
+    n_lig, k_deg = int(n_lig), int(k_deg)
+    if messages.dim() != 2:
+        raise RuntimeError("rs_encode_rows expects (m, K_DEG)")
+    if messages.size(1) != k_deg:
+        raise RuntimeError("messages's second dim must equal k_deg")
+    if k_deg < 2 or k_deg & (k_deg - 1) or n_lig & (n_lig - 1) or n_lig < k_deg:
+        raise RuntimeError("rs_encode_rows: k_deg, n_lig must be powers of 2 with n_lig >= k_deg >= 2")
+    m = messages.size(0)
+    coeffs = messages.clone()
+    if m:
+        ntt_inverse_batched(coeffs)
+    out = torch.zeros((m, n_lig), dtype=_U64, device=messages.device)
+    out[:, :k_deg] = coeffs
+    if m:
+        ntt_forward_batched(out)
+    return out
+
+
+def encode_rows(messages, k_deg, n_lig, *, master_seed=None, row_offset=0, need_polys=True,
+                need_codewords=True):
+    """Fused Ligero row encode (the whole of prover/core.py:746-802 in three kernel passes).
+
+    messages (m, ELL) -> (row_polys (m, K) or None, codewords (m, N) or None).  Slots
+    [ELL, K) are filled with the row_prg pad when master_seed is given, else with zeros
+    (the layergkr convention).  Bit-identical to padding + ntt_inverse_batched +
+    gl_mul by 7^l + zero-extension + ntt_forward_batched."""
+    _chk_u64(messages, "messages")
+    if messages.dim() != 2:
+        raise RuntimeError("encode_rows expects (m, ELL)")
+    m, ell = messages.shape
+    dev = messages.device
+    polys = torch.empty((m, k_deg), dtype=_U64, device=dev) if need_polys else None
+    codes = torch.empty((m, n_lig), dtype=_U64, device=dev) if need_codewords else None
+    seed = None
+    if master_seed is not None:
+        if not (master_seed.is_cuda and master_seed.dtype == torch.uint8 and master_seed.numel() == 32):
+            raise RuntimeError("master_seed must be a 32-byte CUDA uint8 tensor")
+        seed = master_seed.contiguous()
+    with torch.cuda.device(dev):
+        nb = LIB.vi_encode_scratch_bytes(m, k_deg, n_lig)
+        s = scratch(nb, dev) if nb else None
+        check(LIB.vi_encode_rows(ptr(messages), m, ell, k_deg, n_lig, 1 if seed is not None else 0,
+                                 ptr(seed), int(row_offset), ptr(polys), ptr(codes), ptr(s), nb, stream_ptr()))
+    return polys, codes
+
+
+# ---- polynomials ---------------------------------------------------------------------
+def poly_eval(coeffs, points):
+    """Horner evaluation; coeffs (d,) -> (k,) or (m, d) -> (m, k)."""
+    _chk_u64(coeffs, "coeffs"); _chk_u64(points, "points")
+    if points.dim() != 1:
+        raise RuntimeError("points must be 1-D")
+    one_d = coeffs.dim() == 1
+    m = 1 if one_d else coeffs.size(0)
+    d = coeffs.size(0 if one_d else 1)
+    k = points.size(0)
+    out = torch.empty((k,) if one_d else (m, k), dtype=_U64, device=coeffs.device)
+    with torch.cuda.device(coeffs.device):
+        check(LIB.vi_poly_eval(ptr(coeffs), m, d, ptr(points), k, ptr(out), stream_ptr()))
+    return out
+
+
+def _next_pow2(n):
+    p = 2
+    while p < n:
+        p *= 2
+    return p
+
+
+def _padded(t, n):
+    out = torch.zeros(t.shape[:-1] + (n,), dtype=_U64, device=t.device)
+    out[..., :t.size(-1)] = t
+    return out
+
+
+def poly_mul(a, b):
+    """Product of two coefficient-form polynomials (via NTT)."""
+    assert a.dim() == 1 and b.dim() == 1
+    if a.numel() == 0 or b.numel() == 0:
+        return torch.empty(0, dtype=_U64, device=a.device)
+    out_len = a.numel() + b.numel() - 1
+    n = _next_pow2(out_len)
+    fa, fb = _padded(a, n), _padded(b, n)
+    ntt_forward(fa)
+    ntt_forward(fb)
+    prod = gl_mul(fa, fb)
+    ntt_inverse(prod)
+    return prod[:out_len].contiguous()
+
+
+def poly_add(a, b):
+    """Length-adapting polynomial add."""
+    assert a.dim() == 1 and b.dim() == 1
+    n = max(a.numel(), b.numel())
+    if n == 0:
+        return torch.empty(0, dtype=_U64, device=a.device)
+    return gl_add(_padded(a, n), _padded(b, n))
+
+
+def poly_mul_batched(A, B):
+    """Row-wise poly_mul of two (m, d) coefficient matrices -> (m, 2d-1)."""
+    assert A.dim() == 2 and B.dim() == 2 and A.shape == B.shape
+    d = A.size(1)
+    out_len = 2 * d - 1
+    n = _next_pow2(out_len)
+    fa, fb = _padded(A, n), _padded(B, n)
+    ntt_forward_batched(fa)
+    ntt_forward_batched(fb)
+    prod = gl_mul(fa, fb)
+    ntt_inverse_batched(prod)
+    return prod[:, :out_len].contiguous()
+
+
+# ---- linear algebra mod P ----------------------------------------------------------------
+def gl_matmul(A, B):
+    _chk_u64(A, "A"); _chk_u64(B, "B")
+    if A.dim() != 2 or B.dim() != 2:
+        raise RuntimeError("gl_matmul: 2-D inputs")
+    if A.size(1) != B.size(0):
+        raise RuntimeError("gl_matmul: inner dim mismatch")
+    Cm = torch.empty((A.size(0), B.size(1)), dtype=_U64, device=A.device)
+    with torch.cuda.device(A.device):
+        check(LIB.vi_gl_matmul(ptr(A), ptr(B), ptr(Cm), A.size(0), A.size(1), B.size(1), stream_ptr()))
+    return Cm
+
+
+def gl_matvec(M, v):
+    _chk_u64(M, "M"); _chk_u64(v, "v")
+    if M.dim() != 2 or v.dim() != 1:
+        raise RuntimeError("gl_matvec: (m,n) @ (n,)")
+    if v.size(0) != M.size(1):
+        raise RuntimeError("gl_matvec: dim mismatch")
+    out = torch.empty((M.size(0),), dtype=_U64, device=M.device)
+    with torch.cuda.device(M.device):
+        check(LIB.vi_gl_matvec(ptr(M), ptr(v), ptr(out), M.size(0), M.size(1), stream_ptr()))
+    return out
+
+
+def gl_spmv(values, col_idx, row_ptr, x, n_rows):
+    """CSR mod-P matvec. row_ptr length must be n_rows + 1."""
+    for t, nm in ((values, "values"), (col_idx, "col_idx"), (row_ptr, "row_ptr"), (x, "x")):
+        _chk_u64(t, nm)
+    n_rows = int(n_rows)
+    if row_ptr.size(0) != n_rows + 1:
+        raise RuntimeError("row_ptr length must be n_rows + 1")
+    y = torch.empty((n_rows,), dtype=_U64, device=values.device)
+    with torch.cuda.device(values.device):
+        check(LIB.vi_gl_spmv(ptr(values), ptr(col_idx), ptr(row_ptr), ptr(x), None, None, 0,
+                             ptr(y), n_rows, stream_ptr()))
+    return y
+
+
+def gl_spmv_challenged(values, col_idx, row_ptr, seed, label, n_rows):
+    """CSR matvec whose dense operand x[cid] = challenge(seed, cid, label) is computed inline."""
+    for t, nm in ((values, "values"), (col_idx, "col_idx"), (row_ptr, "row_ptr")):
+        _chk_u64(t, nm)
+    seed, label = _chk_seed_label(seed, label)
+    n_rows = int(n_rows)
+    if row_ptr.size(0) != n_rows + 1:
+        raise RuntimeError("row_ptr length must be n_rows + 1")
+    y = torch.empty((n_rows,), dtype=_U64, device=values.device)
+    with torch.cuda.device(values.device):
+        check(LIB.vi_gl_spmv(ptr(values), ptr(col_idx), ptr(row_ptr), None, ptr(seed), ptr(label),
+                             label.numel(), ptr(y), n_rows, stream_ptr()))
+    return y
+
+
+def _band(kind, out, out_off, flat_lo, n_slots, p, desc, aux0, aux1, chal_buf, aux_n, seed, label):
+    _chk_u64(out, "out")
+    seed, label = _chk_seed_label(seed, label)
+    if int(n_slots) == 0:
+        return
+    p = [int(v) & ((1 << 64) - 1) for v in p] + [0] * (4 - len(p))
+    with torch.cuda.device(out.device):
+        check(LIB.vi_interp_band(kind, ptr(out), int(out_off), int(flat_lo), int(n_slots), p[0], p[1], p[2], p[3],
+                                 ptr(desc), ptr(aux0), ptr(aux1), ptr(chal_buf), int(aux_n),
+                                 ptr(seed), ptr(label), label.numel(), stream_ptr()))
+
+
+def interp_band(out, out_off, flat_lo, n_slots, desc, tblA, tblB, chal_buf, seed, label):
+    """Descriptor-interpreter band evaluation, accumulated in place into `out`
+    (desc[24] layout of prover/cuda_primitives.py:593-604)."""
+    for t, nm in ((desc, "desc"), (tblA, "tblA"), (tblB, "tblB"), (chal_buf, "chal_buf")):
+        _chk_u64(t, nm)
+    if desc.numel() != 24:
+        raise RuntimeError("interp_band: desc must be u64[24]")
+    _band(0, out, out_off, flat_lo, n_slots, [], desc, tblA, tblB, chal_buf, 0, seed, label)
+
+
+def interp_band_causal_id(out, out_off, flat_lo, n_slots, base, m, h, coef, seed, label):
+    _band(1, out, out_off, flat_lo, n_slots, [base, m, h, coef], None, None, None, None, 0, seed, label)
+
+
+def interp_band_causal_c2(out, out_off, flat_lo, n_slots, base, h, coef, seed, label):
+    _band(2, out, out_off, flat_lo, n_slots, [base, h, coef], None, None, None, None, 0, seed, label)
+
+
+def interp_band_embed(out, out_off, flat_lo, n_slots, base, d, rows_per_w, ell, token_ids, seed, label):
+    if not (token_ids.is_cuda and token_ids.dtype == torch.int64):
+        raise RuntimeError("token_ids must be a CUDA int64 tensor")
+    tok = token_ids.contiguous()
+    _band(3, out, out_off, flat_lo, n_slots, [base, d, rows_per_w, ell], None, tok, None, None,
+          tok.numel(), seed, label)
+
+
+def interp_band_rope_x(out, out_off, flat_lo, n_slots, base, H, d_h, cos_t, sin_t, seed, label):
+    if cos_t.dtype != _U64 or sin_t.dtype != _U64 or not cos_t.is_cuda or not sin_t.is_cuda:
+        raise RuntimeError("cos_t / sin_t must be CUDA uint64 tensors")
+    _band(4, out, out_off, flat_lo, n_slots, [base, H, d_h], None, cos_t.contiguous(), sin_t.contiguous(),
+          None, 0, seed, label)
+
+
+def challenge_at(seed, label, cids):
+    """challenge(seed, cid, label) for an arbitrary uint64 cid tensor (any shape)."""
+    seed, label = _chk_seed_label(seed, label)
+    if not (cids.is_cuda and cids.dtype == _U64):
+        raise RuntimeError("cids must be a CUDA uint64 tensor")
+    cc = cids.contiguous()
+    out = torch.empty_like(cc)
+    with torch.cuda.device(cc.device):
+        check(LIB.vi_challenge(ptr(seed), ptr(label), label.numel(), ptr(cc), cc.numel(), ptr(out), stream_ptr()))
+    return out
+
+
+def challenge_vec(seed, label, n):
+    """r[i] = challenge(seed, i, label) for i in [0, n)."""
+    n = int(n)
+    if n == 0:
+        return torch.empty(0, dtype=_U64, device="cuda")
+    seed, label = _chk_seed_label(seed, label)
+    if not 0 <= n < (1 << 31):
+        raise RuntimeError("challenge_vec n must be in [0, 2^31)")
+    out = torch.empty((n,), dtype=_U64, device=seed.device)
+    with torch.cuda.device(seed.device):
+        check(LIB.vi_challenge(ptr(seed), ptr(label), label.numel(), None, n, ptr(out), stream_ptr()))
+    return out
+
+
+# ---- BLAKE3 column hash + Merkle --------------------------------------------------------------
+_BLAKE3_CHUNK_ROWS = 128
+
+
+def hash_columns_streamed(matrix):
+    """(m, n) uint64 -> (n, 32) uint8 BLAKE3 column digests. No row cap."""
+    _chk_u64(matrix, "matrix")
+    if matrix.dim() != 2:
+        raise RuntimeError("expected (m, n) matrix")
+    m, n = matrix.shape
+    out = torch.empty((n, 32), dtype=torch.uint8, device=matrix.device)
+    with torch.cuda.device(matrix.device):
+        nb = LIB.vi_hash_columns_scratch_bytes(m, n)
+        s = scratch(nb, matrix.device, "hash") if nb else None
+        check(LIB.vi_hash_columns(ptr(matrix), m, n, ptr(out), ptr(s), nb, stream_ptr()))
+    return out
+
+
+def row_prg(master_seed, row_offset, n_rows, slack_per_row):
+    """(n_rows, slack) uint64 ZK pad: out[r, k] = u64le(BLAKE3(master_seed ||
+    (row_offset+r)_le8 || k_le8)[0:8]) mod P.  Stateless and deterministic."""
+    assert isinstance(master_seed, torch.Tensor)
+    if master_seed.dtype != torch.uint8:
+        raise RuntimeError("master_seed must be uint8")
+    if master_seed.numel() != 32:
+        raise RuntimeError("master_seed must be 32 bytes")
+    if not master_seed.is_cuda:
+        raise RuntimeError("master_seed must be on CUDA")
+    if not master_seed.is_contiguous():
+        raise RuntimeError("master_seed must be contiguous")
+    n_rows, slack = int(n_rows), int(slack_per_row)
+    if n_rows < 0 or slack < 0:
+        raise RuntimeError("row_prg: negative size")
+    out = torch.empty((n_rows, slack), dtype=_U64, device=master_seed.device)
+    with torch.cuda.device(master_seed.device):
+        check(LIB.vi_row_prg(ptr(master_seed), int(row_offset), None, n_rows, slack, ptr(out), stream_ptr()))
+    return out
+
+
+def row_prg_indexed(master_seed, row_indices, slack_per_row):
+    """row_prg for an arbitrary list of absolute row indices (CUDA uint64 tensor)."""
+    if not (master_seed.dtype == torch.uint8 and master_seed.numel() == 32 and master_seed.is_cuda):
+        raise RuntimeError("master_seed must be a 32-byte CUDA uint8 tensor")
+    if not (row_indices.dtype == _U64 and row_indices.is_cuda and row_indices.is_contiguous()):
+        raise RuntimeError("row_indices must be a contiguous CUDA uint64 tensor")
+    n_rows, slack = row_indices.numel(), int(slack_per_row)
+    out = torch.empty((n_rows, slack), dtype=_U64, device=master_seed.device)
+    with torch.cuda.device(master_seed.device):
+        check(LIB.vi_row_prg(ptr(master_seed.contiguous()), 0, ptr(row_indices), n_rows, slack, ptr(out),
+                             stream_ptr()))
+    return out
+
+
+class MerkleColumnAccumulator:
+    """Incremental column hash of a tall matrix supplied in row chunks; gives the same
+    digests as `hash_columns_streamed` on the concatenation without ever holding it.
+
+    Same contract as the reference class (prover/cuda_primitives.py:1297-1385):
+    `n_total_rows` (> 128) is announced up front, `update()` takes any number of rows,
+    `finalize()` returns the (n_cols, 32) digests.  Differences are internal: whole
+    128-row groups of an update go to the GPU in ONE launch straight from the caller's
+    tensor (no per-chunk `.contiguous()` copies), at most 127 rows are buffered between
+    calls, and the device state holds one chaining value per pending subtree level."""
+
+    def __init__(self, n_cols: int, n_total_rows: int):
+        assert n_total_rows > _BLAKE3_CHUNK_ROWS, (
+            "MerkleColumnAccumulator requires multi-BLAKE3-chunk input; "
+            "for <=128 rows use hash_columns_streamed directly")
+        self.n_cols = int(n_cols)
+        self.n_total_rows = int(n_total_rows)
+        self.n_chunks_total = (self.n_total_rows + _BLAKE3_CHUNK_ROWS - 1) // _BLAKE3_CHUNK_ROWS
+        nb = LIB.vi_hash_stream_state_bytes(self.n_cols, self.n_total_rows)
+        self._state = torch.empty(max(nb, 1), dtype=torch.uint8, device="cuda")
+        self._digests = torch.empty((self.n_cols, 32), dtype=torch.uint8, device="cuda")
+        self._tail = torch.empty((_BLAKE3_CHUNK_ROWS, self.n_cols), dtype=_U64, device="cuda")
+        self._tail_rows = 0
+        self._rows_fed = 0      # rows handed to the kernel so far (multiple of 128 until the end)
+        self._rows_seen = 0     # rows received through update()
+
+    def _feed(self, rows, n):
+        with torch.cuda.device(self._state.device):
+            check(LIB.vi_hash_stream_update(ptr(self._state), self.n_cols, self.n_total_rows, self._rows_fed,
+                                            ptr(rows), n, ptr(self._digests), stream_ptr()))
+        self._rows_fed += n
+
+    def update(self, rows):
+        """rows: (k, n_cols) uint64, any k >= 0."""
+        assert rows.dtype == _U64 and rows.is_cuda
+        assert rows.dim() == 2 and rows.size(1) == self.n_cols
+        k = rows.size(0)
+        if k == 0:
+            return
+        assert self._rows_seen + k <= self.n_total_rows, "more rows than n_total_rows"
+        rows = rows.contiguous()
+        self._rows_seen += k
+        pos = 0
+        if self._tail_rows:
+            take = min(_BLAKE3_CHUNK_ROWS - self._tail_rows, k)
+            self._tail[self._tail_rows:self._tail_rows + take] = rows[:take]
+            self._tail_rows += take
+            pos = take
+            if self._tail_rows == _BLAKE3_CHUNK_ROWS:
+                self._feed(self._tail, _BLAKE3_CHUNK_ROWS)
+                self._tail_rows = 0
+        last = self._rows_seen == self.n_total_rows
+        body = ((k - pos) // _BLAKE3_CHUNK_ROWS) * _BLAKE3_CHUNK_ROWS
+        rest = k - pos - body
+        if body:
+            self._feed(rows[pos:pos + body], body)
+            pos += body
+        if rest:
+            self._tail[self._tail_rows:self._tail_rows + rest] = rows[pos:]
+            self._tail_rows += rest
+        if last and self._tail_rows:
+            self._feed(self._tail, self._tail_rows)
+            self._tail_rows = 0
+
+    def finalize(self):
+        """Returns (n_cols, 32) uint8 column digests."""
+        assert self._rows_fed == self.n_total_rows, (
+            f"expected {self.n_total_rows} rows, saw {self._rows_seen}")
+        return self._digests
+
+
+def merkle_build_blake3(leaves):
+    """(N, 32) uint8 leaves -> (root (32,) uint8, levels); levels[0] is `leaves`,
+    levels[-1] has shape (1, 32).  All upper levels come from one library call and are
+    views into one buffer."""
+    assert leaves.dim() == 2 and leaves.size(1) == 32
+    assert leaves.dtype == torch.uint8 and leaves.is_cuda
+    n = leaves.size(0)
+    levels = [leaves]
+    src = leaves.contiguous()
+    total = LIB.vi_merkle_upper_nodes(n)
+    upper = torch.empty((max(total, 1), 32), dtype=torch.uint8, device=leaves.device)
+    with torch.cuda.device(leaves.device):
+        check(LIB.vi_merkle_build(ptr(src), n, ptr(upper), stream_ptr()))
+    off = 0
+    while n > 1:
+        n = (n + 1) // 2
+        levels.append(upper[off:off + n])
+        off += n
+    root = levels[-1].reshape(-1)[:32].clone()
+    return root, levels
+
+
+def commit_rows(messages, k_deg, n_lig, *, master_seed=None, row_offset=0):
+    """Encode + column-hash + Merkle in one call: (m, ELL) messages -> (root, levels,
+    codewords).  Composition of encode_rows, hash_columns_streamed, merkle_build_blake3."""
+    _, codes = encode_rows(messages, k_deg, n_lig, master_seed=master_seed, row_offset=row_offset,
+                           need_polys=False)
+    root, levels = merkle_build_blake3(hash_columns_streamed(codes))
+    return root, levels, codes
+
+
+# ---- LogUp ------------------------------------------------------------------------------------
+_range_table_cache: dict = {}
+
+
+def _is_range_table(table):
+    """True when table[i] == i for all i (probed once per (pointer, length))."""
+    key = (table.data_ptr(), table.numel())
+    hit = _range_table_cache.get(key)
+    if hit is None:
+        ref = torch.arange(table.numel(), dtype=torch.int64, device=table.device).view(_U64)
+        hit = bool(torch.equal(table, ref))
+        _range_table_cache[key] = hit
+    return hit
+
+
+def lookup_multiplicities(x, table):
+    """mult[j] = #{i : x[i] == table[j]}; x values not in the table contribute nothing."""
+    _chk_u64(x, "x"); _chk_u64(table, "table")
+    if x.dim() != 1 or table.dim() != 1:
+        raise RuntimeError("lookup_multiplicities: 1-D inputs")
+    mult = torch.zeros((table.size(0),), dtype=_U64, device=x.device)
+    with torch.cuda.device(x.device):
+        check(LIB.vi_lookup_multiplicities(ptr(x), x.numel(), ptr(table), table.numel(), ptr(mult), stream_ptr()))
+    return mult
+
+
+def lookup_multiplicities_into(x, table, mult, label=""):
+    """mult[j] += #{i : x[i] == table[j]} (accumulating).  Range tables [0, T) take an
+    O(1)-per-element path."""
+    _chk_u64(x, "x"); _chk_u64(table, "table"); _chk_u64(mult, "mult")
+    if x.dim() != 1 or table.dim() != 1 or mult.dim() != 1:
+        raise RuntimeError("lookup_multiplicities_into: 1-D inputs")
+    if mult.numel() != table.numel():
+        raise RuntimeError("mult length must match table")
+    tbl = None if _is_range_table(table) else table
+    with torch.cuda.device(x.device):
+        check(LIB.vi_lookup_multiplicities(ptr(x), x.numel(), ptr(tbl), table.numel(), ptr(mult), stream_ptr()))
+
+
+# ---- compatibility with the reference's private module handle ----------------------------------
+class _Module:
+    """Stands in for the reference's JIT extension object (`_ensure_compiled()`), for code
+    that reaches for merkle_one_level or the stream-hash trio directly."""
+
+    _stream_pos: dict = {}
+
+    @staticmethod
+    def merkle_one_level(nodes_u32):
+        if not (nodes_u32.is_cuda and nodes_u32.dtype == torch.uint32 and nodes_u32.is_contiguous()
+                and nodes_u32.dim() == 2 and nodes_u32.size(1) == 8):
+            raise RuntimeError("merkle_one_level expects a contiguous CUDA (N, 8) uint32 tensor")
+        n = nodes_u32.size(0)
+        if n % 2:
+            raise RuntimeError("merkle_one_level: n must be even (caller duplicates last leaf if needed)")
+        out = torch.empty((n // 2, 8), dtype=torch.uint32, device=nodes_u32.device)
+        with torch.cuda.device(nodes_u32.device):
+            check(LIB.vi_merkle_level(ptr(nodes_u32), n, ptr(out), stream_ptr()))
+        return out
+
+    # The stream trio keeps the chunk counter on the host (all columns advance together).
+    _STATE_LEVELS = 40
+
+    @classmethod
+    def hash_columns_stream_init(cls, n_cols):
+        st = torch.empty((int(n_cols), cls._STATE_LEVELS * 32), dtype=torch.uint8, device="cuda")
+        cls._stream_pos[st.data_ptr()] = 0
+        return st
+
+    @classmethod
+    def hash_columns_stream_update(cls, states, chunk, is_last_chunk, n_chunks_total):
+        _chk_u64(chunk, "chunk")
+        if chunk.dim() != 2 or chunk.size(0) > _BLAKE3_CHUNK_ROWS:
+            raise RuntimeError("chunk must fit within one BLAKE3 chunk (128 rows)")
+        done = cls._stream_pos[states.data_ptr()]
+        n = chunk.size(0)
+        n_cols = chunk.size(1)
+        total = done + n if is_last_chunk else int(n_chunks_total) * _BLAKE3_CHUNK_ROWS
+        dig = torch.empty((n_cols, 32), dtype=torch.uint8, device=chunk.device)
+        with torch.cuda.device(chunk.device):
+            check(LIB.vi_hash_stream_update(ptr(states), n_cols, total, done, ptr(chunk), n, ptr(dig), stream_ptr()))
+        cls._stream_pos[states.data_ptr()] = done + n
+        if is_last_chunk:
+            cls._stream_pos[("digest", states.data_ptr())] = dig
+
+    @classmethod
+    def hash_columns_stream_finalize(cls, states, n_cols, n_chunks_total):
+        return cls._stream_pos.pop(("digest", states.data_ptr()))
+
+
+def _ensure_compiled():
+    return _Module
+
+
+def _self_test():
+    """Small known-answer check (field identities + an NTT round trip)."""
+    a = torch.tensor([7, 13, 99, 1 << 60, (1 << 63) | 1], dtype=_U64, device="cuda")
+    b = torch.tensor([5, 17, 21, 7, (1 << 32) | 3], dtype=_U64, device="cuda")
+    want = [(int(x) * int(y)) % P for x, y in zip(a.cpu().tolist(), b.cpu().tolist())]
+    assert gl_mul(a, b).cpu().tolist() == want
+    x = torch.arange(1, 1025, dtype=torch.int64, device="cuda").to(_U64)
+    y = x.clone()
+    ntt_forward(y)
+    ntt_inverse(y)
+    assert torch.equal(x, y)
+    print("verinf_b200.cuda_primitives: self-test passed")
+
+
+if __name__ == "__main__":
+    _self_test()

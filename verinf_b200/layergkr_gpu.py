@@ -1,0 +1,146 @@
+"""Device-resident versions of the three layergkr/gpu.py entry points that sit on the hot
+path: `encode_batch_ntt`, `hash_and_tree`, `prove_terms_gpu` (same names, argument meaning
+and return values as layergkr/gpu.py:141-203, 274-289, 350-410).
+
+`prove_terms_gpu` keeps the reference's per-round `coin` callback, but each round is one
+fused fold+evaluate launch and one small D2H copy of the deg+1 samples, instead of ~10
+elementwise launches and a host sync per sample point.
+"""
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import cuda_primitives as cp
+from ._lib import LIB, check, ptr, scratch, stream_ptr
+
+P = cp.P
+_MAX_FAC = 4
+
+
+def encode_batch_ntt(cfg, messages):
+    """messages: (rows, <=K_DEG) device tensor or Python rows of <= ELL values -> (rows, N_LIG)
+    codewords on the coset 7*<w_N>; unused slots up to K_DEG are zero (layergkr convention)."""
+    if not hasattr(messages, "shape"):
+        src = [list(m) + [0] * (cfg.ELL - len(m)) for m in messages]
+        messages = torch.tensor(src, dtype=torch.uint64, device="cuda")
+    _, codes = cp.encode_rows(messages.contiguous(), cfg.K_DEG, cfg.N_LIG, need_polys=False)
+    return codes
+
+
+def hash_and_tree(cfg, mat):
+    """Column digests + Merkle tree on the device; returns (root bytes, levels tensors)."""
+    dig = cp.hash_columns_streamed(mat.contiguous())
+    root_t, levels_t = cp.merkle_build_blake3(dig)
+    return bytes(root_t.cpu().tolist()), levels_t
+
+
+class SumcheckProblem:
+    """Tables and term structure of a sum-of-products sumcheck, resident on the device."""
+
+    def __init__(self, tables: torch.Tensor, terms: Sequence):
+        """tables: (n_tables, size) uint64 CUDA tensor (folded in place by `round`);
+        terms: [(coef, [table indices])]."""
+        assert tables.dtype == torch.uint64 and tables.is_cuda and tables.dim() == 2 and tables.is_contiguous()
+        self.tables = tables
+        self.size = tables.size(1)
+        self.n_tables = tables.size(0)
+        self.deg = max(len(f) for _, f in terms)
+        self._coefs = np.array([c % P for c, _ in terms], dtype=np.uint64)
+        self._nfac = np.array([len(f) for _, f in terms], dtype=np.int32)
+        fac = np.zeros((len(terms), _MAX_FAC), dtype=np.int32)
+        for t, (_, f) in enumerate(terms):
+            if len(f) > _MAX_FAC:
+                raise RuntimeError(f"sumcheck: at most {_MAX_FAC} factors per term")
+            fac[t, :len(f)] = f
+        self._fac = fac
+        self.n_terms = len(terms)
+        dev = tables.device
+        self._out = torch.empty(8, dtype=torch.uint64, device=dev)
+        self._partials = scratch(LIB.vi_sumcheck_scratch_bytes(), dev, "sumcheck")
+        self._host = torch.empty(8, dtype=torch.uint64).pin_memory()
+
+    def _args(self):
+        return (self.tables.size(1), self.n_tables, self.size, self.n_terms,
+                self._coefs.ctypes.data, self._nfac.ctypes.data, self._fac.ctypes.data)
+
+    def _read(self, n) -> List[int]:
+        self._host.copy_(self._out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return [int(v) for v in self._host[:n].tolist()]
+
+    def claim(self) -> int:
+        with torch.cuda.device(self.tables.device):
+            check(LIB.vi_sumcheck_claim(ptr(self.tables), *self._args(), ptr(self._out), ptr(self._partials),
+                                        stream_ptr()))
+        return self._read(1)[0]
+
+    def round(self, r: Optional[int]) -> Optional[List[int]]:
+        """Fold with r (None on the first round), then return the samples g(0..deg) of the
+        current tables, or None once the tables are down to a single entry."""
+        fold = r is not None
+        with torch.cuda.device(self.tables.device):
+            check(LIB.vi_sumcheck_round(ptr(self.tables), *self._args(), int(fold), (r or 0) % P,
+                                        ptr(self._out), ptr(self._partials), stream_ptr()))
+        if fold:
+            self.size //= 2
+        if self.size < 2:
+            return None
+        return self._read(self.deg + 1)
+
+    def finals(self) -> List[int]:
+        return [int(v) for v in self.tables[:, 0].cpu().tolist()]
+
+
+def _poly_eval(coeffs, x, p):
+    acc = 0
+    for c in reversed(coeffs):
+        acc = (acc * x + c) % p
+    return acc
+
+
+def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=None, mu0: int = 0):
+    """Sumcheck prover for sum_x sum_k c_k prod_j f_kj(x): returns
+    (claim, round_polys [[(x, y), ...] per round], challenges, final_mask).
+
+    `terms` is [(coef, [factor, ...])] where a factor is a Python sequence or a 1-D uint64
+    CUDA tensor; factors that are the same object share one device table."""
+    assert field_p == P
+    uniq, index, plan = [], {}, []
+    for c, fs in terms:
+        idx = []
+        for f in fs:
+            key = id(f)
+            if key not in index:
+                index[key] = len(uniq)
+                uniq.append(f)
+            idx.append(index[key])
+        plan.append((c % P, idx))
+    rows = []
+    for f in uniq:
+        if isinstance(f, torch.Tensor):
+            rows.append(f.to(device="cuda").reshape(-1))
+        else:
+            rows.append(torch.tensor([int(x) % P for x in f], dtype=torch.uint64, device="cuda"))
+    tables = torch.stack([r.view(torch.int64) for r in rows]).view(torch.uint64).contiguous()
+    prob = SumcheckProblem(tables, plan)
+    n_rounds = prob.size.bit_length() - 1
+    deg = prob.deg
+    mu = mu0 % P
+    claim = (prob.claim() + mu) % P
+    round_polys, challenges = [], []
+    r = None
+    for rnd in range(n_rounds):
+        ys = prob.round(r)
+        samples = list(enumerate(ys))
+        if mask is not None:
+            h = mask(deg, mu)
+            samples = [(x, (y + _poly_eval(h, x, P)) % P) for x, y in samples]
+        round_polys.append(samples)
+        r = coin(rnd) % P
+        challenges.append(r)
+        if mask is not None:
+            mu = _poly_eval(h, r, P)
+    if n_rounds:
+        prob.round(r)          # last fold: tables collapse to their evaluation at the challenge point
+    return claim, round_polys, challenges, mu

@@ -1,0 +1,22 @@
+"""Registers the drop-in modules under the names the reference's callers import.
+
+The reference binds to its CUDA layer by module name — `from cuda_primitives import ...`
+with prover/ pushed to sys.path[0], `from kquant_cuda import kquant_to_field`, and
+`from prover import cuda_primitives as cp` in layergkr — so path order cannot win.
+`install()` pre-registers this package's modules in sys.modules under all four names;
+call it before importing any reference module and the untouched core.py / tape.py /
+layergkr pick up the sm_100a kernels.
+"""
+import sys
+
+
+def install() -> None:
+    from . import cuda_primitives, kquant_cuda
+    for name in ("cuda_primitives", "prover.cuda_primitives"):
+        sys.modules[name] = cuda_primitives
+    for name in ("kquant_cuda", "prover.kquant_cuda"):
+        sys.modules[name] = kquant_cuda
+    pkg = sys.modules.get("prover")
+    if pkg is not None:
+        pkg.cuda_primitives = cuda_primitives
+        pkg.kquant_cuda = kquant_cuda
