@@ -140,6 +140,7 @@ int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, int64_t d_out
  * A problem is n_tables multilinear tables of `size` entries (power of two; entry i of
  * table k at tables[k*stride + i]) and n_terms products: term t = coefs[t] *
  * prod_{j < nfac[t]} table[fac[t*4 + j]]  (at most 8 tables, 8 terms, 4 factors).
+ * coefs, nfac and fac are small HOST arrays (n_terms, n_terms, n_terms*4 entries).
  *   vi_sumcheck_claim   sum over the hypercube of all terms -> out[0]
  *   vi_sumcheck_round   if fold != 0 first folds every table with challenge r
  *                       (f'[i] = f[i] + r*(f[half+i] - f[i]), size -> size/2, in place),
@@ -181,6 +182,16 @@ int vi_interp_band(int kind, uint64_t* out, int64_t out_off, int64_t flat_lo, in
                    const uint64_t* desc_dev, const void* aux0, const void* aux1, const uint64_t* chal_buf,
                    int64_t aux_n, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,
                    void* stream);
+
+/* ---- per-kernel timing ------------------------------------------------------------
+ * CUDA events recorded around every launch on the launching stream while enabled (the
+ * reference's nearest equivalent is its LIGERO_EPHASE event sums, prover/core.py:1139-1165).
+ * vi_profile_enable(1) clears the counters; vi_profile_read waits for the recorded events
+ * and returns total device milliseconds and launch count of one kernel tag. */
+void vi_profile_enable(int on);
+int vi_profile_num_tags(void);
+const char* vi_profile_tag_name(int tag);
+int vi_profile_read(int tag, double* total_ms, int64_t* launches);
 
 #ifdef __cplusplus
 }

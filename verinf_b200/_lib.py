@@ -47,6 +47,10 @@ SIGNATURES = {
     "vi_lookup_multiplicities": (_int, [_p, _i64, _p, _i64, _p, _p]),
     "vi_interp_band": (_int, [_int, _p, _i64, _i64, _i64, _u64, _u64, _u64, _u64,
                               _p, _p, _p, _p, _i64, _p, _p, _int, _p]),
+    "vi_profile_enable": (None, [_int]),
+    "vi_profile_num_tags": (_int, []),
+    "vi_profile_tag_name": (C.c_char_p, [_int]),
+    "vi_profile_read": (_int, [_int, C.POINTER(_dbl), C.POINTER(_i64)]),
 }
 
 
@@ -92,3 +96,18 @@ def scratch(nbytes: int, device, tag: str = "main") -> torch.Tensor:
         buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
+
+
+def profile_enable(on: bool) -> None:
+    LIB.vi_profile_enable(int(on))
+
+
+def profile_read() -> dict:
+    """{kernel tag: (total device ms, launches)} for every tag with at least one launch."""
+    out = {}
+    for t in range(LIB.vi_profile_num_tags()):
+        ms, n = _dbl(0), _i64(0)
+        check(LIB.vi_profile_read(t, C.byref(ms), C.byref(n)))
+        if n.value:
+            out[LIB.vi_profile_tag_name(t).decode()] = (ms.value, n.value)
+    return out

@@ -18,6 +18,15 @@ namespace vi {
 int fail(int code, const char* fmt, ...);   // records the message, returns code
 int check_launch(const char* what);          // cudaGetLastError -> status
 
+// Optional per-kernel timing with CUDA events on the launching stream (off by default).
+enum ProfTag { PROF_ENC_PASS1 = 0, PROF_ENC_MID, PROF_ENC_PASS3, PROF_NTT_PASS, PROF_HASH, PROF_MERKLE,
+               PROF_PRG, PROF_KQUANT, PROF_SUMCHECK, PROF_NTAGS };
+struct ProfScope {
+    int tag; cudaStream_t st; void* rec;
+    ProfScope(int tag, cudaStream_t st);
+    ~ProfScope();
+};
+
 inline bool is_pow2(int64_t n) { return n > 0 && (n & (n - 1)) == 0; }
 inline int ilog2(int64_t n) { int l = 0; while ((int64_t(1) << l) < n) ++l; return l; }
 

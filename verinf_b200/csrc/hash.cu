@@ -164,6 +164,7 @@ extern "C" int vi_hash_stream_update(void* state, int64_t ncols, int64_t total_r
     a.total_chunks = total_rows == 0 ? 1 : (uint64_t)((total_rows + CHUNK_ROWS - 1) / CHUNK_ROWS);
     a.state = (uint32_t*)state; a.digests = (uint32_t*)digests;
     const int block = 128;
+    vi::ProfScope prof(vi::PROF_HASH, (cudaStream_t)stream);
     k_hash_stream<<<(unsigned)((ncols + block - 1) / block), block, 0, (cudaStream_t)stream>>>(a);
     return vi::check_launch("k_hash_stream");
 }
@@ -197,6 +198,7 @@ extern "C" int vi_merkle_level(const uint8_t* nodes, int64_t n_nodes, uint8_t* p
     VI_REQUIRE(((uintptr_t)nodes & 3) == 0 && ((uintptr_t)parents & 3) == 0, "merkle: buffers must be 4-byte aligned");
     int64_t n_out = (n_nodes + 1) / 2;
     const int block = 128;
+    vi::ProfScope prof(vi::PROF_MERKLE, (cudaStream_t)stream);
     k_merkle_level<<<(unsigned)((n_out + block - 1) / block), block, 0, (cudaStream_t)stream>>>(
         (const uint32_t*)nodes, n_nodes, (uint32_t*)parents, n_out);
     return vi::check_launch("k_merkle_level");
@@ -225,6 +227,7 @@ extern "C" int vi_row_prg(const uint8_t* seed_dev, int64_t row_off, const uint64
     const int block = 256;
     int64_t grid = (total + block - 1) / block;
     if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "row_prg: too many elements");
+    vi::ProfScope prof(vi::PROF_PRG, (cudaStream_t)stream);
     k_row_prg<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(seed_dev, row_off, rows_dev, n_rows, slack, out);
     return vi::check_launch("k_row_prg");
 }

@@ -32,6 +32,7 @@ extern "C" int vi_kquant_to_field(const uint8_t* raw, int64_t n_blocks, int qtyp
     int64_t g = (n_blocks + 7) / 8;
     unsigned grid = (unsigned)(g < 148 * 32 ? g : 148 * 32);
     cudaStream_t st = (cudaStream_t)stream;
+    vi::ProfScope prof(vi::PROF_KQUANT, st);
     if (qtype == 4) k_kquant<4><<<grid, 256, 0, st>>>(raw, n_blocks, S, out);
     else if (qtype == 5) k_kquant<5><<<grid, 256, 0, st>>>(raw, n_blocks, S, out);
     else k_kquant<6><<<grid, 256, 0, st>>>(raw, n_blocks, S, out);

@@ -428,21 +428,22 @@ int tile_threads(int logL, int logC) {
 size_t tile_smem(int logL, int logC) { return (size_t)(1 << logL) * ((1 << logC) + 1) * 8; }
 
 template <int LOGL, bool INV, int MODE>
-int launch_pass_t(const PassArgs& a, int64_t items, cudaStream_t st) {
+int launch_pass_t(const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
     size_t smem = tile_smem(LOGL, a.logC);
     auto fn = k_pass<LOGL, INV, MODE>;
     if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = items * a.tiles_per_item;
     if (grid <= 0) return VI_OK;
     if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "tile grid too large (%lld)", (long long)grid);
+    vi::ProfScope prof(tag, st);
     fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
     return vi::check_launch("k_pass");
 }
 
 template <bool INV, int MODE>
-int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st) {
+int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
     switch (logL) {
-#define VI_CASE(x) case x: return launch_pass_t<x, INV, MODE>(a, items, st);
+#define VI_CASE(x) case x: return launch_pass_t<x, INV, MODE>(a, items, st, tag);
         VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
         VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
 #undef VI_CASE
@@ -450,12 +451,12 @@ int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st) {
     return vi::fail(VI_ERR_LIMIT, "unsupported tile length 2^%d", logL);
 }
 
-int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaStream_t st) {
+int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaStream_t st, int tag) {
     a.tiles_per_item = (a.ncols + (1 << a.logC) - 1) >> a.logC;
     int rc = get_tw(int64_t(1) << logL, &a.twL);
     if (rc) return rc;
-    if (inv) return mode ? launch_pass_l<true, 1>(logL, a, items, st) : launch_pass_l<true, 0>(logL, a, items, st);
-    return mode ? launch_pass_l<false, 1>(logL, a, items, st) : launch_pass_l<false, 0>(logL, a, items, st);
+    if (inv) return mode ? launch_pass_l<true, 1>(logL, a, items, st, tag) : launch_pass_l<true, 0>(logL, a, items, st, tag);
+    return mode ? launch_pass_l<false, 1>(logL, a, items, st, tag) : launch_pass_l<false, 0>(logL, a, items, st, tag);
 }
 
 template <int LOGL>
@@ -466,6 +467,7 @@ int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
     int64_t grid = items * a.tiles_per_item;
     if (grid <= 0) return VI_OK;
     if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "tile grid too large (%lld)", (long long)grid);
+    vi::ProfScope prof(vi::PROF_ENC_MID, st);
     fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
     return vi::check_launch("k_encode_mid");
 }
@@ -486,24 +488,6 @@ uint64_t inv_pow2(int log) {   // 2^-log mod p
 constexpr int64_t L2_CHUNK_BYTES = 40ll << 20;   // keep a chunk's intermediates L2-resident
 
 }  // namespace
-
-namespace vi {
-static thread_local char g_err[512] = "";
-int fail(int code, const char* fmt, ...) {
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(g_err, sizeof(g_err), fmt, ap);
-    va_end(ap);
-    return code;
-}
-int check_launch(const char* what) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(VI_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
-    return VI_OK;
-}
-}  // namespace vi
-
-extern "C" const char* vi_last_error(void) { return vi::g_err; }
 
 extern "C" int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n) {
     if (n <= (int64_t(1) << MAX_LOGL) || m <= 0) return 0;
@@ -533,7 +517,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         a.in_item = 0; a.in_idx = 1; a.in_col = n;
         a.out_item = 0; a.out_k = 1; a.out_col = n;
         a.twN = nullptr; a.scale = scale; a.out_via_smem = 1; a.src_kind = SRC_PLAIN;
-        return launch_pass(logn, inv, 1, a, 1, st);
+        return launch_pass(logn, inv, 1, a, 1, st, vi::PROF_NTT_PASS);
     }
     const int log1 = (logn + 1) / 2, log2 = logn - log1;
     const int64_t n1 = int64_t(1) << log1, n2 = int64_t(1) << log2;
@@ -552,7 +536,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         a.in_item = n; a.in_idx = n2; a.in_col = 1;
         a.out_item = n; a.out_k = n2; a.out_col = 1;
         a.twN = twn; a.twN_mask = (uint32_t)(n - 1); a.scale = 1; a.out_via_smem = 0; a.src_kind = SRC_PLAIN;
-        rc = launch_pass(log1, inv, 0, a, cnt, st);
+        rc = launch_pass(log1, inv, 0, a, cnt, st, vi::PROF_NTT_PASS);
         if (rc) return rc;
         PassArgs b{};
         b.in = (const uint64_t*)scratch; b.out = rows + r0 * n;
@@ -561,7 +545,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         b.in_item = n; b.in_idx = 1; b.in_col = n2;
         b.out_item = n; b.out_k = n1; b.out_col = 1;
         b.twN = nullptr; b.scale = scale; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
-        rc = launch_pass(log2, inv, 1, b, cnt, st);
+        rc = launch_pass(log2, inv, 1, b, cnt, st, vi::PROF_NTT_PASS);
         if (rc) return rc;
     }
     return VI_OK;
@@ -625,7 +609,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
             a.kq_dout = kq->d_out; a.kq_din = kq->d_in; a.kq_first_row = kq->first_row + r0;
         } a.pad_mode = (ell < k) ? pad_mode : 0; a.row_off = row_off + r0;
         a.seed = seed_dev32;
-        rc = launch_pass(log1, true, 0, a, cnt, st);
+        rc = launch_pass(log1, true, 0, a, cnt, st, vi::PROF_ENC_PASS1);
         if (rc) return rc;
         // pass 2: inverse step 2 (length n2) + twist + forward step 1 for every coset
         MidArgs mid{};
@@ -646,7 +630,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         b.in_item = n; b.in_idx = 1; b.in_col = n1;
         b.out_item = n; b.out_k = rho * n2; b.out_col = 1;
         b.twN = nullptr; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
-        rc = launch_pass(log1, false, 1, b, cnt, st);
+        rc = launch_pass(log1, false, 1, b, cnt, st, vi::PROF_ENC_PASS3);
         if (rc) return rc;
     }
     return VI_OK;

@@ -220,6 +220,7 @@ extern "C" int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_t
     VI_REQUIRE(out && partials, "sumcheck: null output/scratch");
     cudaStream_t st = (cudaStream_t)stream;
     int g = grid_for(size);
+    vi::ProfScope prof(vi::PROF_SUMCHECK, st);
     k_sumcheck<0><<<g, BLOCK, 0, st>>>(pb, size, 0, (uint64_t*)partials);
     k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, 1, out);
     return vi::check_launch("k_sumcheck<claim>");
@@ -236,6 +237,7 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
     VI_REQUIRE(r < vgl::P, "sumcheck: challenge not canonical");
     VI_REQUIRE(out && partials, "sumcheck: null output/scratch");
     cudaStream_t st = (cudaStream_t)stream;
+    vi::ProfScope prof(vi::PROF_SUMCHECK, st);
     if (!fold) {
         int g = grid_for(size / 2);
         k_sumcheck<1><<<g, BLOCK, 0, st>>>(pb, size, 0, (uint64_t*)partials);
