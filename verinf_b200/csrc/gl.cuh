@@ -4,6 +4,11 @@
 // (prover/kernels/goldilocks.cuh:28-81): canonical inputs in [0, p) give the
 // canonical result.  The 128-bit product is reduced with 2^64 = 2^32 - 1 and
 // 2^96 = -1 (mod p).
+//
+// The device versions are written on 32-bit limbs with explicit carry chains
+// (add.cc / subc): on sm_100a the integer ALU pipe issues half a warp per cycle and is
+// the limiter of the NTT kernels, so every op is the shortest carry-chain sequence
+// found: sub = 5 instructions, add = neg + sub = 7, reduce128 = 17.
 #pragma once
 #include <cstdint>
 
@@ -12,23 +17,22 @@ namespace vgl {
 constexpr uint64_t P = 0xFFFFFFFF00000001ull;
 constexpr uint64_t EPS = 0xFFFFFFFFull;   // 2^32 - 1 = 2^64 mod p
 
-__host__ __device__ __forceinline__ uint64_t add(uint64_t a, uint64_t b) {
+__host__ __device__ __forceinline__ uint64_t pack(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+
+// ---- portable versions (host, and the oracle of the PTX versions) -----------------
+__host__ __device__ __forceinline__ uint64_t add_c(uint64_t a, uint64_t b) {
     uint64_t s = a + b;
     if (s < a) s += EPS;          // wrapped past 2^64: +2^64 = +EPS (mod p)
     if (s >= P) s -= P;
     return s;
 }
-
-__host__ __device__ __forceinline__ uint64_t sub(uint64_t a, uint64_t b) {
+__host__ __device__ __forceinline__ uint64_t sub_c(uint64_t a, uint64_t b) {
     uint64_t d = a - b;
     if (a < b) d -= EPS;          // borrowed 2^64: -2^64 = -EPS (mod p)
     return d;
 }
-
-__host__ __device__ __forceinline__ uint64_t neg(uint64_t a) { return a == 0 ? 0 : P - a; }
-
 // (hi:lo) mod p, canonical.  hi = hh*2^32 + hl:  x = lo - hh + hl*(2^32-1).
-__host__ __device__ __forceinline__ uint64_t reduce128(uint64_t lo, uint64_t hi) {
+__host__ __device__ __forceinline__ uint64_t reduce128_c(uint64_t lo, uint64_t hi) {
     uint64_t hh = hi >> 32, hl = hi & EPS;
     uint64_t t0 = lo - hh;
     if (lo < hh) t0 -= EPS;
@@ -39,9 +43,99 @@ __host__ __device__ __forceinline__ uint64_t reduce128(uint64_t lo, uint64_t hi)
     return r;
 }
 
-__device__ __forceinline__ uint64_t mul(uint64_t a, uint64_t b) {
-    return reduce128(a * b, __umul64hi(a, b));
+// a - b mod p for canonical a, b (also exact for b == p): 5 instructions
+__host__ __device__ __forceinline__ uint64_t sub(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    uint32_t d0, d1, m;
+    asm("sub.cc.u32 %0, %3, %5;\n\t"
+        "subc.cc.u32 %1, %4, %6;\n\t"
+        "subc.u32 %2, 0, 0;\n\t"          // m = borrow ? 0xffffffff : 0
+        "sub.cc.u32 %0, %0, %2;\n\t"      // d -= borrow ? EPS : 0
+        "subc.u32 %1, %1, 0;"
+        : "=&r"(d0), "=&r"(d1), "=&r"(m)
+        : "r"((uint32_t)a), "r"((uint32_t)(a >> 32)), "r"((uint32_t)b), "r"((uint32_t)(b >> 32)));
+    return pack(d0, d1);
+#else
+    return sub_c(a, b);
+#endif
 }
+
+__host__ __device__ __forceinline__ uint64_t add(uint64_t a, uint64_t b) {
+#ifdef __CUDA_ARCH__
+    // a + b = a - (p - b); p - b is p for b == 0, which sub() accepts as a subtrahend: 7 instructions
+    uint32_t n0, n1;
+    asm("sub.cc.u32 %0, 1, %2;\n\t"
+        "subc.u32 %1, 0xffffffff, %3;"
+        : "=&r"(n0), "=&r"(n1) : "r"((uint32_t)b), "r"((uint32_t)(b >> 32)));
+    return sub(a, pack(n0, n1));
+#else
+    return add_c(a, b);
+#endif
+}
+
+// (hi:lo) mod p, canonical: 17 instructions on the device
+__host__ __device__ __forceinline__ uint64_t reduce128(uint64_t lo, uint64_t hi) {
+#ifdef __CUDA_ARCH__
+    uint32_t r0, r1;
+    asm("{\n\t.reg .u32 m, e0, e1;\n\t.reg .pred q;\n\t"
+        "sub.cc.u32 %0, %2, %5;\n\t"       // t = lo - hh
+        "subc.cc.u32 %1, %3, 0;\n\t"
+        "subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 %0, %0, m;\n\t"        // t -= borrow ? EPS : 0   (cannot borrow again)
+        "subc.u32 %1, %1, 0;\n\t"
+        "sub.cc.u32 e0, 0, %4;\n\t"        // e = hl*EPS = (hl<<32) - hl
+        "subc.u32 e1, %4, 0;\n\t"
+        "add.cc.u32 %0, %0, e0;\n\t"       // r = t + e
+        "addc.cc.u32 %1, %1, e1;\n\t"
+        "addc.u32 m, 0, 0;\n\t"            // m = carry ? 0xffffffff : 0 (carry of an add chain must be
+        "neg.s32 m, m;\n\t"                //     read with addc: subc after add.cc sees it inverted)
+        "add.cc.u32 %0, %0, m;\n\t"        // r += carry ? EPS : 0     (cannot carry again)
+        "addc.u32 %1, %1, 0;\n\t"
+        "setp.eq.u32 q, %1, 0xffffffff;\n\t"   // r >= p  <=>  hi == 2^32-1 and lo != 0; then r - p = lo - 1
+        "setp.ne.and.u32 q, %0, 0, q;\n\t"
+        "@q mov.u32 %1, 0;\n\t"
+        "@q add.u32 %0, %0, 0xffffffff;\n\t}"
+        : "=&r"(r0), "=&r"(r1)
+        : "r"((uint32_t)lo), "r"((uint32_t)(lo >> 32)), "r"((uint32_t)hi), "r"((uint32_t)(hi >> 32)));
+    return pack(r0, r1);
+#else
+    return reduce128_c(lo, hi);
+#endif
+}
+
+#ifdef __CUDA_ARCH__
+// (l1:l0) + h*(2^32-1) mod p, canonical; (l1:l0) is any u64, h any u32: 12 instructions
+__device__ __forceinline__ uint64_t add_mul_eps(uint32_t l0, uint32_t l1, uint32_t h) {
+    uint32_t r0, r1;
+    asm("{\n\t.reg .u32 m, e0, e1;\n\t.reg .pred q;\n\t"
+        "sub.cc.u32 e0, 0, %4;\n\t"
+        "subc.u32 e1, %4, 0;\n\t"
+        "add.cc.u32 %0, %2, e0;\n\t"
+        "addc.cc.u32 %1, %3, e1;\n\t"
+        "addc.u32 m, 0, 0;\n\t"
+        "neg.s32 m, m;\n\t"
+        "add.cc.u32 %0, %0, m;\n\t"
+        "addc.u32 %1, %1, 0;\n\t"
+        "setp.eq.u32 q, %1, 0xffffffff;\n\t"
+        "setp.ne.and.u32 q, %0, 0, q;\n\t"
+        "@q mov.u32 %1, 0;\n\t"
+        "@q add.u32 %0, %0, 0xffffffff;\n\t}"
+        : "=&r"(r0), "=&r"(r1) : "r"(l0), "r"(l1), "r"(h));
+    return pack(r0, r1);
+}
+#endif
+
+// full 64x64 -> 128 product on 32-bit limbs (4 wide multiply-adds), then reduce
+__device__ __forceinline__ uint64_t mul(uint64_t a, uint64_t b) {
+    const uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
+    uint64_t t = (uint64_t)a0 * b0;                          // bits 0..63
+    uint64_t u = (uint64_t)a0 * b1 + (t >> 32);              // no overflow: (2^32-1)^2 + 2^32-1 < 2^64
+    uint64_t v = (uint64_t)a1 * b0 + (uint32_t)u;            // idem
+    uint64_t w = (uint64_t)a1 * b1 + (u >> 32) + (v >> 32);  // bits 64..127
+    return reduce128(pack((uint32_t)t, (uint32_t)v), w);
+}
+
+__host__ __device__ __forceinline__ uint64_t neg(uint64_t a) { return a == 0 ? 0 : P - a; }
 
 __device__ __forceinline__ uint64_t pow(uint64_t base, uint64_t e) {
     uint64_t r = 1;
@@ -56,29 +150,40 @@ __device__ __forceinline__ uint64_t pow(uint64_t base, uint64_t e) {
 // x * 2^S mod p for a compile-time 0 <= S < 96 (x canonical -> canonical).
 // Every 2^k-th root of unity with k <= 6 is a power of two in this field
 // (2 has order 192), so radix-<=64 butterflies multiply by shifts only.
+// With phi = 2^32 (phi^2 = phi - 1, phi^3 = -1) the shifted value is a short sum of limbs:
+//   S <  32: (l1:l0) + l2*(2^32-1)                       with (l2:l1:l0) = x << S
+//   S >= 64: w2*(2^32-1) - (w4:w3)                       with (w4:w3:w2) = x << (S-64)
+//   else   : the general 128-bit reduction.
 template <int S>
 __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
     static_assert(S >= 0 && S < 96, "shift out of range");
+#ifdef __CUDA_ARCH__
     if constexpr (S == 0) {
         return x;
+    } else if constexpr (S < 32) {
+        uint64_t lo = x << S;
+        return add_mul_eps((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)(x >> (64 - S)));
     } else if constexpr (S < 64) {
-        uint64_t lo = x << S, hi = x >> (64 - S);
-        return reduce128(lo, hi);
-    } else if constexpr (S == 64) {
-        return reduce128(0, x);
+        return reduce128(x << S, x >> (64 - S));
     } else {
-        // x*2^S = (y_hi*2^64 + y_lo) * 2^64 with y = x << (S-64) (< 2^96);
-        // 2^128 = -2^32, so the result is reduce128(0, y_lo) - y_hi*2^32.
         constexpr int T = S - 64;
-        uint64_t ylo = x << T, yhi = x >> (64 - T);
-        return sub(reduce128(0, ylo), yhi << 32);
+        const uint32_t w2 = (uint32_t)(x << T);
+        const uint64_t h = x >> (32 - T);                  // (w4:w3) < 2^63: canonical
+        uint32_t e0, e1;
+        asm("sub.cc.u32 %0, 0, %2;\n\t"                    // e = w2*EPS (canonical)
+            "subc.u32 %1, %2, 0;"
+            : "=&r"(e0), "=&r"(e1) : "r"(w2));
+        return sub(pack(e0, e1), h);
     }
+#else
+    return x;
+#endif
 }
 
 // host-side helpers used when building twiddle tables
 inline uint64_t hmul(uint64_t a, uint64_t b) {
     unsigned __int128 v = (unsigned __int128)a * b;
-    return reduce128((uint64_t)v, (uint64_t)(v >> 64));
+    return reduce128_c((uint64_t)v, (uint64_t)(v >> 64));
 }
 inline uint64_t hpow(uint64_t b, uint64_t e) {
     uint64_t r = 1;

@@ -17,8 +17,10 @@
 //  * The encode runs three passes per row chunk: iNTT step 1 (message + pad
 //    loader), iNTT step 2 fused with the coset twist and step 1 of all rho coset
 //    NTTs, and step 2 of the coset NTTs writing the interleaved codeword.
+#include <cstdlib>
 #include <map>
 #include <mutex>
+#include <tuple>
 #include <vector>
 
 #include "../../include/verinf_b200.h"
@@ -168,8 +170,7 @@ struct PassArgs {
     int64_t in_item, in_idx, in_col;
     int64_t out_item, out_k, out_col;
     const uint64_t* twL;     // w_L^e, e < L
-    const uint64_t* twN;     // w_n^e, e < n (four-step factor w_n^(col*k)) or null
-    uint32_t twN_mask;
+    const uint64_t* fs;      // four-step factors, fs[k*ncols + col] = w_n^(+-col*k), or null
     uint64_t scale;          // multiply outputs by this unless 1
     int out_via_smem;        // outputs are contiguous along k: transpose through smem
     // SRC_MSG loader: input element (item=row, pos, col) is slot j = pos*in_idx + col of the
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(512) k_pass(PassArgs a) {
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
         uint32_t k = SC::last_k(j, w);
-        if (a.twN) v[j] = mul(v[j], tw_at<INV>(a.twN, (uint32_t)colg * k, a.twN_mask));
+        if (a.fs && valid) v[j] = mul(v[j], __ldg(a.fs + (int64_t)k * a.ncols + colg));
         if (a.scale != 1) v[j] = mul(v[j], a.scale);
     }
     if (!a.out_via_smem) {
@@ -292,7 +293,7 @@ struct MidArgs {
     int rho;
     int64_t K;
     const uint64_t* twL;   // w_L^e
-    const uint64_t* twK;   // w_K^e
+    const uint64_t* fsK;   // forward four-step factors, fsK[m1*n1 + l2] = w_K^(l2*m1)
     const uint64_t* twist; // (rho, K): (7*w_N^t)^l
     uint64_t k_inv;
 };
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
                 uint32_t m1 = SF::last_k(j, w);
-                uint64_t x = mul(v[j], __ldg(a.twK + (uint32_t)colg * m1));
+                uint64_t x = mul(v[j], __ldg(a.fsK + (int64_t)m1 * a.n1 + colg));
                 dst2[((int64_t)m1 * a.rho + t) * a.n1] = x;
             }
         }
@@ -363,6 +364,7 @@ __global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
 struct DevTables {
     std::map<int64_t, uint64_t*> tw;                          // n -> w_n^e, e < n
     std::map<std::pair<int64_t, int64_t>, uint64_t*> twist;   // (K, N) -> (rho, K)
+    std::map<std::tuple<int64_t, int64_t, bool>, uint64_t*> fs;   // (n, ncols, inverse) -> four-step factors
 };
 std::mutex g_mu;
 std::map<int, DevTables> g_tables;
@@ -381,6 +383,34 @@ int get_tw(int64_t n, const uint64_t** out) {
     VI_CUDA(cudaMalloc(&d, (size_t)n * 8));
     VI_CUDA(cudaMemcpy(d, h.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
     T.tw[n] = d;
+    *out = d;
+    return VI_OK;
+}
+
+// four-step factor table for n = ncols*L: fs[k*ncols + c] = w_n^(c*k) (inverse: w_n^(-c*k)),
+// laid out so that the 16 columns of a tile read 128 contiguous bytes per output index k
+int get_fs(int64_t n, int64_t ncols, bool inv, const uint64_t** out) {
+    int dev;
+    VI_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto& T = g_tables[dev];
+    auto key = std::make_tuple(n, ncols, inv);
+    auto it = T.fs.find(key);
+    if (it != T.fs.end()) { *out = it->second; return VI_OK; }
+    const int64_t L = n / ncols;
+    std::vector<uint64_t> h((size_t)n);
+    uint64_t wn = vgl::hpow(7, (vgl::P - 1) / (uint64_t)n);
+    if (inv) wn = vgl::hpow(wn, vgl::P - 2);
+    uint64_t step = 1;                     // w^k
+    for (int64_t k = 0; k < L; ++k) {
+        uint64_t cur = 1;
+        for (int64_t c = 0; c < ncols; ++c) { h[(size_t)(k * ncols + c)] = cur; cur = vgl::hmul(cur, step); }
+        step = vgl::hmul(step, wn);
+    }
+    uint64_t* d = nullptr;
+    VI_CUDA(cudaMalloc(&d, (size_t)n * 8));
+    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
+    T.fs[key] = d;
     *out = d;
     return VI_OK;
 }
@@ -485,14 +515,23 @@ uint64_t inv_pow2(int log) {   // 2^-log mod p
     return vgl::hpow(vgl::hpow(2, (uint64_t)log), vgl::P - 2);
 }
 
-constexpr int64_t L2_CHUNK_BYTES = 40ll << 20;   // keep a chunk's intermediates L2-resident
+// Row-chunk size the *_scratch_bytes helpers recommend (intermediates of one chunk live in the
+// scratch buffer).  VERINF_CHUNK_MB overrides it for experiments.
+int64_t chunk_bytes() {
+    static const int64_t v = [] {
+        const char* e = getenv("VERINF_CHUNK_MB");
+        int64_t mb = e ? atoll(e) : 0;
+        return (mb > 0 ? mb : 40) << 20;
+    }();
+    return v;
+}
 
 }  // namespace
 
 extern "C" int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n) {
     if (n <= (int64_t(1) << MAX_LOGL) || m <= 0) return 0;
     int64_t row = n * 8;
-    int64_t rows = L2_CHUNK_BYTES / row;
+    int64_t rows = chunk_bytes() / row;
     if (rows < 1) rows = 1;
     if (rows > m) rows = m;
     return rows * row;
@@ -516,7 +555,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         a.ncols = m;
         a.in_item = 0; a.in_idx = 1; a.in_col = n;
         a.out_item = 0; a.out_k = 1; a.out_col = n;
-        a.twN = nullptr; a.scale = scale; a.out_via_smem = 1; a.src_kind = SRC_PLAIN;
+        a.fs = nullptr; a.scale = scale; a.out_via_smem = 1; a.src_kind = SRC_PLAIN;
         return launch_pass(logn, inv, 1, a, 1, st, vi::PROF_NTT_PASS);
     }
     const int log1 = (logn + 1) / 2, log2 = logn - log1;
@@ -524,8 +563,8 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
     VI_REQUIRE(scratch != nullptr && scratch_bytes >= n * 8,
                "ntt: scratch of at least %lld bytes required (see vi_ntt_scratch_bytes)", (long long)(n * 8));
     int64_t chunk = scratch_bytes / (n * 8);
-    const uint64_t* twn;
-    int rc = get_tw(n, &twn);
+    const uint64_t* fsn;
+    int rc = get_fs(n, n2, inv, &fsn);
     if (rc) return rc;
     for (int64_t r0 = 0; r0 < m; r0 += chunk) {
         int64_t cnt = m - r0 < chunk ? m - r0 : chunk;
@@ -535,7 +574,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         a.ncols = n2;
         a.in_item = n; a.in_idx = n2; a.in_col = 1;
         a.out_item = n; a.out_k = n2; a.out_col = 1;
-        a.twN = twn; a.twN_mask = (uint32_t)(n - 1); a.scale = 1; a.out_via_smem = 0; a.src_kind = SRC_PLAIN;
+        a.fs = fsn; a.scale = 1; a.out_via_smem = 0; a.src_kind = SRC_PLAIN;
         rc = launch_pass(log1, inv, 0, a, cnt, st, vi::PROF_NTT_PASS);
         if (rc) return rc;
         PassArgs b{};
@@ -544,7 +583,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         b.ncols = n1;
         b.in_item = n; b.in_idx = 1; b.in_col = n2;
         b.out_item = n; b.out_k = n1; b.out_col = 1;
-        b.twN = nullptr; b.scale = scale; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
+        b.fs = nullptr; b.scale = scale; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
         rc = launch_pass(log2, inv, 1, b, cnt, st, vi::PROF_NTT_PASS);
         if (rc) return rc;
     }
@@ -554,7 +593,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
 extern "C" int64_t vi_encode_scratch_bytes(int64_t m, int64_t k, int64_t n) {
     if (m <= 0) return 0;
     int64_t row = (k + n) * 8;
-    int64_t rows = L2_CHUNK_BYTES / row;
+    int64_t rows = chunk_bytes() / row;
     if (rows < 1) rows = 1;
     if (rows > m) rows = m;
     return rows * row;
@@ -587,9 +626,10 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
     VI_REQUIRE(scratch != nullptr && scratch_bytes >= per_row,
                "encode: scratch of at least %lld bytes required (see vi_encode_scratch_bytes)", (long long)per_row);
     int64_t chunk = scratch_bytes / per_row;
-    const uint64_t *twk, *twist = nullptr;
-    int rc = get_tw(k, &twk);
+    const uint64_t *fs_inv, *fs_fwd = nullptr, *twist = nullptr;
+    int rc = get_fs(k, n2, true, &fs_inv);        // inverse step 1: columns j2 (n2 of them), index k1
     if (rc) return rc;
+    if (codes) { rc = get_fs(k, n1, false, &fs_fwd); if (rc) return rc; }   // forward step 1: columns l2 (n1), index m1
     if (codes) { rc = get_twist(k, n, &twist); if (rc) return rc; }
     uint64_t* s1 = (uint64_t*)scratch;
     for (int64_t r0 = 0; r0 < m; r0 += chunk) {
@@ -602,7 +642,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         a.ncols = n2;
         a.in_item = ell; a.in_idx = n2; a.in_col = 1;
         a.out_item = k; a.out_k = n2; a.out_col = 1;
-        a.twN = twk; a.twN_mask = (uint32_t)(k - 1); a.scale = 1; a.out_via_smem = 0;
+        a.fs = fs_inv; a.scale = 1; a.out_via_smem = 0;
         a.src_kind = kq ? SRC_KQ : SRC_MSG; a.ell = ell;
         if (kq) {
             a.kq_raw = kq->raw; a.kq_type = kq->qtype; a.kq_transpose = kq->transpose; a.kq_S = kq->S;
@@ -616,7 +656,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         mid.s1 = s1; mid.polys = polys ? polys + r0 * k : nullptr; mid.s2 = codes ? s2 : nullptr;
         mid.logC = pick_logC(log2, n1);
         mid.n1 = n1; mid.tiles_per_item = (n1 + (1 << mid.logC) - 1) >> mid.logC;
-        mid.rho = (int)rho; mid.K = k; mid.twK = twk; mid.twist = twist; mid.k_inv = inv_pow2(logk);
+        mid.rho = (int)rho; mid.K = k; mid.fsK = fs_fwd; mid.twist = twist; mid.k_inv = inv_pow2(logk);
         rc = get_tw(n2, &mid.twL);
         if (rc) return rc;
         rc = launch_mid(log2, mid, cnt, st);
@@ -629,7 +669,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         b.logC = pick_logC(log1, b.ncols);
         b.in_item = n; b.in_idx = 1; b.in_col = n1;
         b.out_item = n; b.out_k = rho * n2; b.out_col = 1;
-        b.twN = nullptr; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
+        b.fs = nullptr; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
         rc = launch_pass(log1, false, 1, b, cnt, st, vi::PROF_ENC_PASS3);
         if (rc) return rc;
     }
