@@ -92,6 +92,18 @@ int64_t vi_hash_columns_scratch_bytes(int64_t m, int64_t ncols);
 int vi_hash_columns(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* digests,
                     void* scratch, int64_t scratch_bytes, void* stream);
 
+/* Same digests as vi_hash_columns for callers that cannot allocate device memory (no
+ * counterpart in the reference).  The chaining-value state lives in a fixed 8 MiB device
+ * array inside the library instead of caller scratch, so the call performs no cudaMalloc /
+ * cudaFree and takes only inputs and outputs.  Inputs needing more state than
+ * vi_hash_columns_noalloc_max_state_bytes() (= vi_hash_stream_state_bytes(ncols, m) for
+ * m > 128; e.g. 65536 columns x up to 1024 rows) are rejected with an error.  The first
+ * call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ * first call before any stream capture.  All calls on a device share the array: calls
+ * that overlap on the GPU race and must be serialised by the caller. */
+int64_t vi_hash_columns_noalloc_max_state_bytes(void);
+int vi_hash_columns_noalloc(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* digests, void* stream);
+
 /* Streaming form: replaces hash_columns_stream_init/update/finalize and the state
  * machine behind MerkleColumnAccumulator (prover/cuda_primitives.py:813-853,976-987,
  * 1297-1385; prover/kernels/blake3_columns.cuh:184-328).  The state is a caller-owned

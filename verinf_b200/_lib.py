@@ -29,6 +29,8 @@ SIGNATURES = {
     "vi_challenge": (_int, [_p, _p, _int, _p, _i64, _p, _p]),
     "vi_hash_columns_scratch_bytes": (_i64, [_i64, _i64]),
     "vi_hash_columns": (_int, [_p, _i64, _i64, _p, _p, _i64, _p]),
+    "vi_hash_columns_noalloc_max_state_bytes": (_i64, []),
+    "vi_hash_columns_noalloc": (_int, [_p, _i64, _i64, _p, _p]),
     "vi_hash_stream_state_bytes": (_i64, [_i64, _i64]),
     "vi_hash_stream_update": (_int, [_p, _i64, _i64, _i64, _p, _i64, _p, _p]),
     "vi_merkle_upper_nodes": (_i64, [_i64]),

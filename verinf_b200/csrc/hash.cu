@@ -10,6 +10,8 @@
 // size instead of by a stack pointer: level b holds the chaining value of a
 // complete subtree of 2^b chunks (the binary-counter form of BLAKE3's incremental
 // tree), stored [level][word][column] so every access is coalesced.
+#include <mutex>
+
 #include "../../include/verinf_b200.h"
 #include "blake3.cuh"
 #include "common.cuh"
@@ -243,4 +245,60 @@ extern "C" int vi_challenge(const uint8_t* seed_dev, const uint8_t* label_dev, i
     if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "challenge: too many elements");
     k_challenge<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(seed_dev, label_dev, label_len, cids_dev, n, out);
     return vi::check_launch("k_challenge");
+}
+
+// ---------------------------------------------------------------------------
+// Column hash for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the moment they need a column
+// hash: a prover that has already handed every free byte of HBM to its witness and
+// codeword buffers (an allocation would fail or force it to shrink a buffer), code
+// running under a fixed memory budget that forbids driver allocations after start-up,
+// or a latency-critical loop in which an allocation's implicit device synchronisation
+// is not acceptable.  For them the chaining-value state that vi_hash_columns takes as
+// caller scratch lives in the fixed device array below instead.
+//
+// The array belongs to the library image: every GPU that loads the library holds its
+// 8 MiB until the process exits.  All calls (on one device) share it and it keeps the
+// contents of the last call.  Nothing in it has to start at zero - each level of the
+// state is written before it is read within a call - but two calls that overlap on the
+// GPU (different streams, or different host threads) race on it and must be serialised
+// by the caller.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int64_t NOALLOC_STATE_BYTES = int64_t(8) << 20;
+static __device__ __align__(256) unsigned char g_noalloc_state[NOALLOC_STATE_BYTES];
+constexpr int MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" int64_t vi_hash_columns_noalloc_max_state_bytes(void) { return NOALLOC_STATE_BYTES; }
+
+extern "C" int vi_hash_columns_noalloc(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* digests,
+                                       void* stream) {
+    VI_REQUIRE(m >= 0 && ncols >= 0, "hash_columns_noalloc: negative size");
+    if (ncols == 0) return VI_OK;
+    const int64_t need = m > CHUNK_ROWS ? vi_hash_stream_state_bytes(ncols, m) : 0;
+    if (need > NOALLOC_STATE_BYTES)
+        return vi::fail(VI_ERR_LIMIT,
+                        "hash_columns_noalloc: %lld rows x %lld columns need %lld bytes of chaining-value state, "
+                        "the built-in buffer holds %lld; use vi_hash_columns with caller scratch",
+                        (long long)m, (long long)ncols, (long long)need, (long long)NOALLOC_STATE_BYTES);
+    int dev = 0;
+    VI_CUDA(cudaGetDevice(&dev));
+    VI_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "hash_columns_noalloc: device index %d not supported", dev);
+    void* state = nullptr;
+    {
+        // Set-up, once per device, with that device current: in host code the array's name is only a
+        // stand-in for the symbol, so its device address has to be asked for.
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {
+            void* p = nullptr;
+            VI_CUDA(cudaGetSymbolAddress(&p, g_noalloc_state));
+            g_noalloc_ptr[dev] = p;
+        }
+        state = g_noalloc_ptr[dev];
+    }
+    return vi_hash_stream_update(state, ncols, m, 0, mat, m, digests, stream);
 }
