@@ -1,0 +1,111 @@
+// Integer-pipe and field-primitive microbenchmarks for sm_100a.
+//
+// The hot path is bound by integer issue rates that no vendor peak figure covers, so the
+// denominators are measured: register-resident kernels, 8 independent chains per thread, one
+// instruction kind (or one field primitive) per kernel, timed with CUDA events.  Under
+// `ncu --metrics smsp__inst_executed.sum,sm__inst_executed_pipe_alu.sum,sm__inst_executed_pipe_fma.sum`
+// the same binary gives instructions per primitive.
+// Build: python -m verinf_b200.build --microbench ; run: verinf_b200/microbench/int_pipes
+#include <cstdint>
+#include <cstdio>
+#include <cuda_runtime.h>
+
+#include "../csrc/dft_reg.cuh"
+#include "../csrc/gl.cuh"
+
+namespace {
+constexpr int ITERS = 1024, CHAINS = 8, GRID = 148 * 8, BLOCK = 256;
+
+template <int OP>
+__global__ void __launch_bounds__(BLOCK) k_raw(uint32_t* out, uint32_t a0, uint32_t m) {
+    uint32_t x[CHAINS], y[CHAINS];
+    uint64_t z[CHAINS];
+#pragma unroll
+    for (int i = 0; i < CHAINS; ++i) { x[i] = a0 + threadIdx.x + i; y[i] = a0 * 3 + i; z[i] = ((uint64_t)x[i] << 32) | y[i]; }
+    for (int it = 0; it < ITERS; ++it) {
+#pragma unroll
+        for (int i = 0; i < CHAINS; ++i) {
+            if (OP == 0) asm volatile("add.u32 %0, %0, %1;" : "+r"(x[i]) : "r"(y[i]));
+            if (OP == 1) asm volatile("mad.lo.u32 %0, %0, %1, %2;" : "+r"(x[i]) : "r"(m), "r"(y[i]));
+            if (OP == 2) asm volatile("mad.wide.u32 %0, %1, %2, %0;" : "+l"(z[i]) : "r"(x[i]), "r"(m));
+            if (OP == 3) asm volatile("shf.r.wrap.b32 %0, %0, %0, %1;" : "+r"(x[i]) : "r"(m));
+            if (OP == 4) asm volatile("prmt.b32 %0, %0, %0, 0x1032;" : "+r"(x[i]));
+            if (OP == 5) asm volatile("add.cc.u32 %0, %0, %2; addc.u32 %1, %1, %3;" : "+r"(x[i]), "+r"(y[i]) : "r"(m), "r"(a0));
+            if (OP == 6) {
+                asm volatile("add.u32 %0, %0, %1;" : "+r"(x[i]) : "r"(m));
+                asm volatile("mad.lo.u32 %0, %0, %1, %2;" : "+r"(y[i]) : "r"(m), "r"(a0));
+            }
+        }
+    }
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < CHAINS; ++i) acc ^= x[i] ^ y[i] ^ (uint32_t)z[i] ^ (uint32_t)(z[i] >> 32);
+    out[blockIdx.x * BLOCK + threadIdx.x] = acc;
+}
+
+template <int OP>
+__global__ void __launch_bounds__(BLOCK) k_field(uint64_t* out, uint64_t seed) {
+    using namespace vgl;
+    uint64_t v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = (seed * (threadIdx.x + 1 + i * 977) + i) % P;
+    for (int it = 0; it < ITERS / 4; ++it) {
+        if (OP == 0) vdft::dif<4, 4, false>(v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (OP == 1) v[i] = sub(v[i], v[(i + 1) & 15]);
+            if (OP == 2) v[i] = add(v[i], v[(i + 1) & 15]);
+            if (OP == 3) v[i] = mul(v[i], v[(i + 1) & 15]);
+            if (OP == 4) v[i] = mul_pow2<12>(v[i]);
+            if (OP == 5) v[i] = mul_pow2<48>(v[i]);
+            if (OP == 6) v[i] = mul_pow2<72>(v[i]);
+        }
+    }
+    uint64_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc ^= v[i];
+    out[blockIdx.x * BLOCK + threadIdx.x] = acc;
+}
+
+template <class F>
+float time_ms(F launch) {
+    cudaEvent_t a, b;
+    cudaEventCreate(&a); cudaEventCreate(&b);
+    launch(); cudaDeviceSynchronize();
+    cudaEventRecord(a); launch(); cudaEventRecord(b); cudaEventSynchronize(b);
+    float ms = 0; cudaEventElapsedTime(&ms, a, b);
+    cudaEventDestroy(a); cudaEventDestroy(b);
+    return ms;
+}
+}  // namespace
+
+int main() {
+    void* d = nullptr;
+    if (cudaMalloc(&d, (size_t)GRID * BLOCK * 8) != cudaSuccess) { printf("no CUDA device\n"); return 1; }
+    int khz = 0; cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, 0);
+    const double threads = (double)GRID * BLOCK;
+    auto raw = [&](const char* name, int per, float ms) {
+        double ops = threads * ITERS * CHAINS * per;
+        printf("%-28s %8.3f ms %9.1f Gop/s %7.1f ops/clk/SM\n", name, ms, ops / ms / 1e6, ops / (ms * 1e-3) / 148 / (khz * 1e3));
+    };
+    raw("add.u32", 1, time_ms([&] { k_raw<0><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("mad.lo.u32", 1, time_ms([&] { k_raw<1><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("mad.wide.u32", 1, time_ms([&] { k_raw<2><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("shf.r.wrap", 1, time_ms([&] { k_raw<3><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("prmt", 1, time_ms([&] { k_raw<4><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("add.cc + addc", 2, time_ms([&] { k_raw<5><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("add.u32 + mad.lo.u32", 2, time_ms([&] { k_raw<6><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    auto fld = [&](const char* name, int per, float ms) {
+        double ops = threads * (ITERS / 4) * per;
+        printf("%-28s %8.3f ms %9.1f Gop/s\n", name, ms, ops / ms / 1e6);
+    };
+    fld("radix-16 DFT element-stage", 64, time_ms([&] { k_field<0><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("gl sub", 16, time_ms([&] { k_field<1><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("gl add", 16, time_ms([&] { k_field<2><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("gl mul", 16, time_ms([&] { k_field<3><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("gl mul_pow2<12>", 16, time_ms([&] { k_field<4><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("gl mul_pow2<48>", 16, time_ms([&] { k_field<5><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("gl mul_pow2<72>", 16, time_ms([&] { k_field<6><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    cudaFree(d);
+    return 0;
+}
