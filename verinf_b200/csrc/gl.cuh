@@ -150,30 +150,50 @@ __device__ __forceinline__ uint64_t pow(uint64_t base, uint64_t e) {
 // x * 2^S mod p for a compile-time 0 <= S < 96 (x canonical -> canonical).
 // Every 2^k-th root of unity with k <= 6 is a power of two in this field
 // (2 has order 192), so radix-<=64 butterflies multiply by shifts only.
-// With phi = 2^32 (phi^2 = phi - 1, phi^3 = -1) the shifted value is a short sum of limbs:
-//   S <  32: (l1:l0) + l2*(2^32-1)                       with (l2:l1:l0) = x << S
-//   S >= 64: w2*(2^32-1) - (w4:w3)                       with (w4:w3:w2) = x << (S-64)
-//   else   : the general 128-bit reduction.
+// With phi = 2^32 (phi^2 = phi - 1, phi^3 = -1) and (l2:l1:l0) = x << (S mod 32):
+//   S <  32: (l1:l0) + l2*(2^32-1)
+//   S <  64: the general 128-bit reduction of (l2:l1:l0:0)
+//   S >= 64: l0*(2^32-1) - (l2:l1)
+// 2^v for v < 32 read from the constant bank: a multiplier the assembler cannot fold, so the
+// limb shifts below are issued as wide multiply-adds on the FMA pipe instead of funnel shifts on
+// the (saturated) ALU pipe.
+static __constant__ uint32_t POW2_TAB[32] = {
+    1u << 0,  1u << 1,  1u << 2,  1u << 3,  1u << 4,  1u << 5,  1u << 6,  1u << 7,
+    1u << 8,  1u << 9,  1u << 10, 1u << 11, 1u << 12, 1u << 13, 1u << 14, 1u << 15,
+    1u << 16, 1u << 17, 1u << 18, 1u << 19, 1u << 20, 1u << 21, 1u << 22, 1u << 23,
+    1u << 24, 1u << 25, 1u << 26, 1u << 27, 1u << 28, 1u << 29, 1u << 30, 1u << 31};
+
 template <int S>
 __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
     static_assert(S >= 0 && S < 96, "shift out of range");
 #ifdef __CUDA_ARCH__
     if constexpr (S == 0) {
         return x;
-    } else if constexpr (S < 32) {
-        uint64_t lo = x << S;
-        return add_mul_eps((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)(x >> (64 - S)));
-    } else if constexpr (S < 64) {
-        return reduce128(x << S, x >> (64 - S));
     } else {
-        constexpr int T = S - 64;
-        const uint32_t w2 = (uint32_t)(x << T);
-        const uint64_t h = x >> (32 - T);                  // (w4:w3) < 2^63: canonical
-        uint32_t e0, e1;
-        asm("sub.cc.u32 %0, 0, %2;\n\t"                    // e = w2*EPS (canonical)
-            "subc.u32 %1, %2, 0;"
-            : "=&r"(e0), "=&r"(e1) : "r"(w2));
-        return sub(pack(e0, e1), h);
+        constexpr int V = S % 32, U = S / 32;
+        // (l2:l1:l0) = x << V as three 32-bit limbs
+        uint32_t l0 = (uint32_t)x, l1 = (uint32_t)(x >> 32), l2 = 0;
+        if constexpr (V != 0) {
+            const uint32_t c = POW2_TAB[V];
+            uint64_t t, u;
+            asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(l0), "r"(c));
+            asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(u) : "r"(l1), "r"(c), "l"(t >> 32));
+            l0 = (uint32_t)t; l1 = (uint32_t)u; l2 = (uint32_t)(u >> 32);
+        }
+        if constexpr (U == 0) {
+            // l0 + l1 phi + l2 phi^2 = (l1:l0) + l2*(2^32-1)
+            return add_mul_eps(l0, l1, l2);
+        } else if constexpr (U == 1) {
+            // l0 phi + l1 phi^2 + l2 phi^3: the 128-bit value (hi = (l2:l1), lo = (l0:0))
+            return reduce128(pack(0, l0), pack(l1, l2));
+        } else {
+            // l0 phi^2 + l1 phi^3 + l2 phi^4 = l0*(2^32-1) - (l2:l1); (l2:l1) < 2^63 is canonical
+            uint32_t e0, e1;
+            asm("sub.cc.u32 %0, 0, %2;\n\t"
+                "subc.u32 %1, %2, 0;"
+                : "=&r"(e0), "=&r"(e1) : "r"(l0));
+            return sub(pack(e0, e1), pack(l1, l2));
+        }
     }
 #else
     return x;

@@ -131,8 +131,9 @@ struct PassArgs {
     int logC;
     int64_t ncols;           // columns per item
     int64_t tiles_per_item;
-    int64_t in_item, in_idx, in_col;
-    int64_t out_item, out_k, out_col;
+    int64_t in_item, out_item;        // element stride between items (64-bit)
+    uint32_t in_idx, in_col;          // element strides inside a tile (32-bit offsets from the tile base)
+    uint32_t out_k, out_col;
     const uint64_t* twL;     // w_L^e, e < L
     const uint64_t* fs;      // four-step factors, fs[k*ncols + col] = w_n^(+-col*k), or null
     uint64_t scale;          // multiply outputs by this unless 1
@@ -164,14 +165,16 @@ __global__ void __launch_bounds__(512) k_pass(PassArgs a) {
     const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
     const int64_t colg = col0 + col;
     const bool valid = colg < a.ncols;
+    const int ncols_tile = a.ncols - col0 < C ? (int)(a.ncols - col0) : C;   // valid columns of this tile
+    const uint32_t ncols32 = (uint32_t)a.ncols;
     uint64_t v[EPT];
 
     if constexpr (MODE == 0) {
         if (a.src_kind == SRC_PLAIN) {
-            const uint64_t* src = a.in + item * a.in_item + colg * a.in_col;
+            const uint64_t* src = a.in + item * a.in_item + colg * (int64_t)a.in_col;
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
-                v[j] = valid ? src[(int64_t)SC::first_pos(j, w) * a.in_idx] : 0;
+                v[j] = valid ? src[(uint32_t)SC::first_pos(j, w) * a.in_idx] : 0;
         } else {
             const uint64_t* src = a.in + item * a.ell;
             uint32_t seed[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -202,11 +205,10 @@ __global__ void __launch_bounds__(512) k_pass(PassArgs a) {
         }
     } else {
         const int nthr = blockDim.x;
-        const uint64_t* src = a.in + item * a.in_item;
+        const uint64_t* src = a.in + item * a.in_item + col0 * (int64_t)a.in_col;
         for (int e = tid; e < L * C; e += nthr) {
             int idx = e & (L - 1), cl = e >> LOGL;
-            int64_t cg = col0 + cl;
-            sm[idx * CP + cl] = cg < a.ncols ? src[cg * a.in_col + (int64_t)idx * a.in_idx] : 0;
+            sm[idx * CP + cl] = cl < ncols_tile ? src[(uint32_t)cl * a.in_col + (uint32_t)idx * a.in_idx] : 0;
         }
         __syncthreads();
 #pragma unroll
@@ -218,14 +220,14 @@ __global__ void __launch_bounds__(512) k_pass(PassArgs a) {
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
         uint32_t k = SC::last_k(j, w);
-        if (a.fs && valid) v[j] = mul(v[j], __ldg(a.fs + (int64_t)k * a.ncols + colg));
+        if (a.fs && valid) v[j] = mul(v[j], __ldg(a.fs + col0 + (k * ncols32 + (uint32_t)col)));
         if (a.scale != 1) v[j] = mul(v[j], a.scale);
     }
     if (!a.out_via_smem) {
         if (valid) {
-            uint64_t* dst = a.out + item * a.out_item + colg * a.out_col;
+            uint64_t* dst = a.out + item * a.out_item + colg * (int64_t)a.out_col;
 #pragma unroll
-            for (int j = 0; j < EPT; ++j) dst[(int64_t)SC::last_k(j, w) * a.out_k] = v[j];
+            for (int j = 0; j < EPT; ++j) dst[(uint32_t)SC::last_k(j, w) * a.out_k] = v[j];
         }
     } else {
         __syncthreads();
@@ -233,11 +235,10 @@ __global__ void __launch_bounds__(512) k_pass(PassArgs a) {
         for (int j = 0; j < EPT; ++j) sm[SC::last_k(j, w) * CP + col] = v[j];
         __syncthreads();
         const int nthr = blockDim.x;
-        uint64_t* dst = a.out + item * a.out_item;
+        uint64_t* dst = a.out + item * a.out_item + col0 * (int64_t)a.out_col;
         for (int e = tid; e < L * C; e += nthr) {
             int k = e & (L - 1), cl = e >> LOGL;
-            int64_t cg = col0 + cl;
-            if (cg < a.ncols) dst[cg * a.out_col + (int64_t)k * a.out_k] = sm[k * CP + cl];
+            if (cl < ncols_tile) dst[(uint32_t)cl * a.out_col + (uint32_t)k * a.out_k] = sm[k * CP + cl];
         }
     }
 }
@@ -275,14 +276,15 @@ __global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
     const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
     const int64_t colg = col0 + col;
     const bool valid = colg < a.n1;
+    const int ncols_tile = a.n1 - col0 < C ? (int)(a.n1 - col0) : C;
+    const uint32_t n1 = (uint32_t)a.n1, rho = (uint32_t)a.rho;
 
     {
         const int nthr = blockDim.x;
-        const uint64_t* src = a.s1 + item * a.K;
+        const uint64_t* src = a.s1 + item * a.K + col0 * L;
         for (int e = tid; e < L * C; e += nthr) {
             int idx = e & (L - 1), cl = e >> LOGL;
-            int64_t cg = col0 + cl;
-            sm[idx * CP + cl] = cg < a.n1 ? src[cg * L + idx] : 0;
+            sm[idx * CP + cl] = cl < ncols_tile ? src[(uint32_t)(cl * L + idx)] : 0;
         }
         __syncthreads();
     }
@@ -295,19 +297,18 @@ __global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
     if (a.polys && valid) {
         uint64_t* dst = a.polys + item * a.K + colg;
 #pragma unroll
-        for (int j = 0; j < EPT; ++j) dst[(int64_t)SI::last_k(j, w) * a.n1] = c[j];
+        for (int j = 0; j < EPT; ++j) dst[(uint32_t)SI::last_k(j, w) * n1] = c[j];
     }
     if (!a.s2) return;
     uint64_t* dst2 = a.s2 + item * a.K * a.rho + colg;
     for (int t = 0; t < a.rho; ++t) {
-        const uint64_t* tw_t = a.twist + (int64_t)t * a.K;
+        const uint64_t* tw_t = a.twist + (int64_t)t * a.K + colg;
         if (SF::NS > 1) __syncthreads();   // previous coset finished reading the tile
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             // forward register j needs coefficient index l1 = first_pos(j): it is held in c[brev(j)]
-            int l1 = SF::first_pos(j, w);
-            int64_t l = colg + a.n1 * (int64_t)l1;
-            uint64_t tw = valid ? __ldg(tw_t + l) : 0;
+            uint32_t l1 = SF::first_pos(j, w);
+            uint64_t tw = valid ? __ldg(tw_t + n1 * l1) : 0;
             v[j] = mul(c[(j / (1 << LR)) * (1 << LR) + brev(j % (1 << LR), LR)], tw);
         }
         run_stages<LOGL, false, true, 0>(v, sm, CP, col, w, a.twL);
@@ -315,8 +316,8 @@ __global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
                 uint32_t m1 = SF::last_k(j, w);
-                uint64_t x = mul(v[j], __ldg(a.fsK + (int64_t)m1 * a.n1 + colg));
-                dst2[((int64_t)m1 * a.rho + t) * a.n1] = x;
+                uint64_t x = mul(v[j], __ldg(a.fsK + colg + m1 * n1));
+                dst2[(m1 * rho + (uint32_t)t) * n1] = x;
             }
         }
     }
@@ -521,8 +522,8 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         a.in = rows; a.out = rows;
         a.logC = pick_logC(logn, m);
         a.ncols = m;
-        a.in_item = 0; a.in_idx = 1; a.in_col = n;
-        a.out_item = 0; a.out_k = 1; a.out_col = n;
+        a.in_item = 0; a.in_idx = 1; a.in_col = (uint32_t)n;
+        a.out_item = 0; a.out_k = 1; a.out_col = (uint32_t)n;
         a.fs = nullptr; a.scale = scale; a.out_via_smem = 1; a.src_kind = SRC_PLAIN;
         return launch_pass(logn, inv, 1, a, 1, st, vi::PROF_NTT_PASS);
     }
@@ -540,8 +541,8 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         a.in = rows + r0 * n; a.out = (uint64_t*)scratch;
         a.logC = pick_logC(log1, n2);
         a.ncols = n2;
-        a.in_item = n; a.in_idx = n2; a.in_col = 1;
-        a.out_item = n; a.out_k = n2; a.out_col = 1;
+        a.in_item = n; a.in_idx = (uint32_t)n2; a.in_col = 1;
+        a.out_item = n; a.out_k = (uint32_t)n2; a.out_col = 1;
         a.fs = fsn; a.scale = 1; a.out_via_smem = 0; a.src_kind = SRC_PLAIN;
         rc = launch_pass(log1, inv, 0, a, cnt, st, vi::PROF_NTT_PASS);
         if (rc) return rc;
@@ -549,8 +550,8 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
         b.in = (const uint64_t*)scratch; b.out = rows + r0 * n;
         b.logC = pick_logC(log2, n1);
         b.ncols = n1;
-        b.in_item = n; b.in_idx = 1; b.in_col = n2;
-        b.out_item = n; b.out_k = n1; b.out_col = 1;
+        b.in_item = n; b.in_idx = 1; b.in_col = (uint32_t)n2;
+        b.out_item = n; b.out_k = (uint32_t)n1; b.out_col = 1;
         b.fs = nullptr; b.scale = scale; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
         rc = launch_pass(log2, inv, 1, b, cnt, st, vi::PROF_NTT_PASS);
         if (rc) return rc;
@@ -608,8 +609,8 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         a.in = kq ? nullptr : msg + r0 * ell; a.out = s1;
         a.logC = pick_logC(log1, n2);
         a.ncols = n2;
-        a.in_item = ell; a.in_idx = n2; a.in_col = 1;
-        a.out_item = k; a.out_k = n2; a.out_col = 1;
+        a.in_item = ell; a.in_idx = (uint32_t)n2; a.in_col = 1;
+        a.out_item = k; a.out_k = (uint32_t)n2; a.out_col = 1;
         a.fs = fs_inv; a.scale = 1; a.out_via_smem = 0;
         a.src_kind = kq ? SRC_KQ : SRC_MSG; a.ell = ell;
         if (kq) {
@@ -635,8 +636,8 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         b.in = s2; b.out = codes + r0 * n;
         b.ncols = rho * n2;
         b.logC = pick_logC(log1, b.ncols);
-        b.in_item = n; b.in_idx = 1; b.in_col = n1;
-        b.out_item = n; b.out_k = rho * n2; b.out_col = 1;
+        b.in_item = n; b.in_idx = 1; b.in_col = (uint32_t)n1;
+        b.out_item = n; b.out_k = (uint32_t)(rho * n2); b.out_col = 1;
         b.fs = nullptr; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
         rc = launch_pass(log1, false, 1, b, cnt, st, vi::PROF_ENC_PASS3);
         if (rc) return rc;
