@@ -115,6 +115,20 @@ int64_t vi_hash_stream_state_bytes(int64_t ncols, int64_t total_rows);
 int vi_hash_stream_update(void* state, int64_t ncols, int64_t total_rows, int64_t rows_done,
                           const uint64_t* rows, int64_t n_rows, uint8_t* digests, void* stream);
 
+/* Sharded column hash (no counterpart in the reference, which is single-GPU): a rank that
+ * holds a row range made of whole 128-row chunks hashes each aligned block of 2^level chunks
+ * to one non-root sub-tree chaining value per column (vi_hash_subtree; first_chunk is the
+ * block's global chunk index, a multiple of 2^level; only the stream's last chunk may be
+ * short), the (ncols, 32) results of all ranks are gathered in row order, and
+ * vi_hash_merge_subtrees folds them into the same digests vi_hash_columns gives on the whole
+ * matrix.  levels is a HOST array with the level of each gathered block, left to right.
+ * state: vi_hash_subtree_state_bytes(ncols, level) bytes of scratch. */
+int64_t vi_hash_subtree_state_bytes(int64_t ncols, int level);
+int vi_hash_subtree(const uint64_t* rows, int64_t n_rows, int64_t ncols, int64_t first_chunk, int level,
+                    void* state, uint8_t* cv_out, void* stream);
+int vi_hash_merge_subtrees(const uint8_t* cvs, const int32_t* levels, int nblocks, int64_t ncols,
+                           uint8_t* digests, void* stream);
+
 /* ---- Merkle tree ----------------------------------------------------------------
  * replaces merkle_build_blake3 / merkle_one_level (prover/cuda_primitives.py:990-1004,
  * 1388-1401; prover/kernels/merkle.cuh:18-37): parent = BLAKE3-256(left || right) as a

@@ -51,6 +51,8 @@ def lib():
         L.or_sumcheck.argtypes = [p, C.c_int, i64, C.c_int, p, p, p, C.c_int, p, p, p, p]
         L.or_sumcheck.restype = C.c_int
         L.or_commit_rows.argtypes = [p, i64, i64, i64, p]; L.or_commit_rows.restype = None
+        L.or_hash_subtree.argtypes = [p, i64, i64, i64, p]; L.or_hash_subtree.restype = None
+        L.or_hash_merge_subtrees.argtypes = [p, p, C.c_int, i64, p]; L.or_hash_merge_subtrees.restype = C.c_int
         _lib = L
     return _lib
 
@@ -209,3 +211,22 @@ def commit_rows(padded, n_lig) -> bytes:
     root = np.empty(32, dtype=np.uint8)
     lib().or_commit_rows(_ptr(padded), m, k, n_lig, _ptr(root))
     return root.tobytes()
+
+
+def hash_subtree(mat, first_chunk: int):
+    """Non-root sub-tree chaining values (ncols, 32) of a block of whole chunks (see verinf_oracle.c)."""
+    mat = _u64(mat)
+    m, n = mat.shape
+    out = np.empty((n, 32), dtype=np.uint8)
+    lib().or_hash_subtree(_ptr(mat), m, n, int(first_chunk), _ptr(out))
+    return out
+
+
+def hash_merge_subtrees(cvs, levels):
+    cvs = np.ascontiguousarray(np.asarray(cvs, dtype=np.uint8))
+    nb, n, _ = cvs.shape
+    lv = np.ascontiguousarray(np.asarray(levels, dtype=np.int32))
+    out = np.empty((n, 32), dtype=np.uint8)
+    rc = lib().or_hash_merge_subtrees(_ptr(cvs), _ptr(lv), nb, n, _ptr(out))
+    assert rc == 0
+    return out

@@ -231,19 +231,23 @@ static void b3_parent(const uint32_t l[8], const uint32_t r[8], uint32_t root_fl
 }
 
 /* subtree over chunks [c0, c0+n) of the input; n >= 1 */
-static void b3_subtree(const uint8_t* p, size_t len, uint64_t c0, uint64_t n, int is_root, uint32_t out[8]) {
+static void b3_subtree_off(const uint8_t* p, size_t len, uint64_t c0, uint64_t n, int is_root,
+                           uint64_t ctr_off, uint32_t out[8]) {
     if (n == 1) {
         size_t off = (size_t)c0 * 1024, l = len - off < 1024 ? len - off : 1024;
         if (len == 0) l = 0;
-        b3_chunk_cv(p + off, l, c0, is_root ? B3_ROOT : 0, out);
+        b3_chunk_cv(p + off, l, c0 + ctr_off, is_root ? B3_ROOT : 0, out);
         return;
     }
     uint64_t left = 1;
     while (left * 2 < n) left *= 2;
     uint32_t a[8], b[8];
-    b3_subtree(p, len, c0, left, 0, a);
-    b3_subtree(p, len, c0 + left, n - left, 0, b);
+    b3_subtree_off(p, len, c0, left, 0, ctr_off, a);
+    b3_subtree_off(p, len, c0 + left, n - left, 0, ctr_off, b);
     b3_parent(a, b, is_root ? B3_ROOT : 0, out);
+}
+static void b3_subtree(const uint8_t* p, size_t len, uint64_t c0, uint64_t n, int is_root, uint32_t out[8]) {
+    b3_subtree_off(p, len, c0, n, is_root, 0, out);
 }
 
 void or_blake3(const uint8_t* data, int64_t len, uint8_t out[32]) {
@@ -513,4 +517,60 @@ void or_commit_rows(const uint64_t* padded, int64_t m, int64_t K, int64_t N, uin
     or_merkle_levels(dig, N, lv);
     memcpy(root, lv + (or_merkle_total_nodes(N) - 1) * 32, 32);
     free(codes); free(dig); free(lv);
+}
+
+/* ------------------------------------------------------------------ */
+/* Sharded column hash (no counterpart in the reference; BLAKE3's tree  */
+/* rule applied to a row range).  Non-root chaining value of the        */
+/* complete sub-tree formed by the chunks of `mat` (n_rows rows =       */
+/* 2^level chunks, only the last may be short), whose first chunk has   */
+/* global index first_chunk.  out: (ncols, 32).                         */
+/* ------------------------------------------------------------------ */
+void or_hash_subtree(const uint64_t* mat, int64_t n_rows, int64_t ncols, int64_t first_chunk, uint8_t* out) {
+    uint64_t nchunks = ((uint64_t)n_rows + 127) / 128;
+    #pragma omp parallel
+    {
+        uint8_t* col = (uint8_t*)malloc((size_t)n_rows * 8);
+        #pragma omp for schedule(static)
+        for (int64_t j = 0; j < ncols; ++j) {
+            for (int64_t i = 0; i < n_rows; ++i) {
+                uint64_t v = mat[i * ncols + j];
+                for (int b = 0; b < 8; ++b) col[i * 8 + b] = (uint8_t)(v >> (8 * b));
+            }
+            uint32_t h[8];
+            b3_subtree_off(col, (size_t)n_rows * 8, 0, nchunks, 0, (uint64_t)first_chunk, h);
+            for (int i = 0; i < 8; ++i)
+                for (int b = 0; b < 4; ++b) out[j * 32 + 4 * i + b] = (uint8_t)(h[i] >> (8 * b));
+        }
+        free(col);
+    }
+}
+
+/* Fold gathered sub-tree values (nblocks, ncols, 32), block sizes 2^levels[i] chunks, left to  */
+/* right, into the column digests: equal-sized neighbours merge as parents, the last block is   */
+/* not merged eagerly, the remaining ones fold right to left and the last merge is the root.    */
+int or_hash_merge_subtrees(const uint8_t* cvs, const int32_t* levels, int nblocks, int64_t ncols, uint8_t* out) {
+    if (nblocks < 2) return 1;
+    #pragma omp parallel for schedule(static)
+    for (int64_t j = 0; j < ncols; ++j) {
+        uint32_t st[64][8]; int lv[64]; int sp = 0;
+        for (int i = 0; i < nblocks; ++i) {
+            const uint8_t* p = cvs + ((int64_t)i * ncols + j) * 32;
+            for (int w = 0; w < 8; ++w)
+                st[sp][w] = (uint32_t)p[4 * w] | ((uint32_t)p[4 * w + 1] << 8) | ((uint32_t)p[4 * w + 2] << 16) | ((uint32_t)p[4 * w + 3] << 24);
+            lv[sp++] = levels[i];
+            if (i == nblocks - 1) break;
+            while (sp >= 2 && lv[sp - 1] == lv[sp - 2]) {
+                uint32_t o[8]; b3_parent(st[sp - 2], st[sp - 1], 0, o);
+                --sp; memcpy(st[sp - 1], o, 32); ++lv[sp - 1];
+            }
+        }
+        while (sp >= 2) {
+            uint32_t o[8]; b3_parent(st[sp - 2], st[sp - 1], sp == 2 ? B3_ROOT : 0, o);
+            --sp; memcpy(st[sp - 1], o, 32);
+        }
+        for (int i = 0; i < 8; ++i)
+            for (int b = 0; b < 4; ++b) out[j * 32 + 4 * i + b] = (uint8_t)(st[0][i] >> (8 * b));
+    }
+    return 0;
 }

@@ -515,3 +515,32 @@ def test_interp_bands(cp):
         hi, lo = divmod(3 + s, 5)
         cid = 70 + hi * 10 + lo
         assert int(got2[s]) == 9 * ((ch(cid) + ch(cid + 100)) % P) % P
+
+
+# ---------------------------------------------------------------- sharded column hash ---
+@pytest.mark.parametrize("m,n,world", [(1024, 300, 2), (4096, 64, 8), (1000, 77, 3), (700, 40, 4), (129, 9, 2)])
+def test_sharded_hash_emulated_ranks(cp, m, n, world):
+    """sub-tree chaining values of every rank's aligned blocks, folded, equal the whole-matrix digests"""
+    from verinf_b200 import distributed as D
+    rng = np.random.default_rng(m + n)
+    a = rnd_field(rng, (m, n))
+    t = dev(a)
+    be = D.CudaBackend(0, 0)
+    cvs, levels = [], []
+    for r0, r1 in D.split_rows(m, world):
+        for b0, cnt, lvl in D.aligned_blocks(r0, r1):
+            cv = be.hash_subtree(t[b0:b0 + cnt], b0 // 128, lvl)
+            assert np.array_equal(cv.cpu().numpy(), oracle.hash_subtree(a[b0:b0 + cnt], b0 // 128))
+            cvs.append(cv)
+            levels.append(lvl)
+    got = be.merge(torch.stack(cvs).contiguous(), levels)
+    assert np.array_equal(got.cpu().numpy(), oracle.hash_columns(a))
+
+
+def test_commit_rows_sharded_single_process(cp):
+    from verinf_b200 import distributed as D
+    rng = np.random.default_rng(8)
+    msg = dev(rnd_field(rng, (600, 100)))
+    root, levels, codes = D.commit_rows_sharded(msg, 600, D.CudaBackend(128, 512))
+    want_root, _, want_codes = cp.commit_rows(msg, 128, 512)
+    assert torch.equal(root, want_root) and torch.equal(codes.view(torch.int64), want_codes.view(torch.int64))

@@ -33,6 +33,9 @@ SIGNATURES = {
     "vi_hash_columns_noalloc": (_int, [_p, _i64, _i64, _p, _p]),
     "vi_hash_stream_state_bytes": (_i64, [_i64, _i64]),
     "vi_hash_stream_update": (_int, [_p, _i64, _i64, _i64, _p, _i64, _p, _p]),
+    "vi_hash_subtree_state_bytes": (_i64, [_i64, _int]),
+    "vi_hash_subtree": (_int, [_p, _i64, _i64, _i64, _int, _p, _p, _p]),
+    "vi_hash_merge_subtrees": (_int, [_p, _p, _int, _i64, _p, _p]),
     "vi_merkle_upper_nodes": (_i64, [_i64]),
     "vi_merkle_build": (_int, [_p, _i64, _p, _p]),
     "vi_merkle_level": (_int, [_p, _i64, _p, _p]),

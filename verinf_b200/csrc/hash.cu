@@ -26,6 +26,7 @@ struct StreamArgs {
     int64_t ncols;
     int64_t n_rows;         // rows in this call
     uint64_t count0;        // chunks hashed before this call
+    uint64_t ctr_base;      // added to the chunk index to form the BLAKE3 chunk counter (sub-tree hashing)
     uint64_t total_chunks;  // chunks of the whole stream (>= 1)
     uint32_t* state;        // [level][8][ncols]
     uint32_t* digests;      // (ncols, 8) words; written by the call that ends the stream
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(128) k_hash_stream(StreamArgs a) {
             }
             uint32_t flags = (b == 0 ? vb3::CHUNK_START : 0) |
                              (b == nb - 1 ? (vb3::CHUNK_END | (single ? vb3::ROOT : 0)) : 0);
-            vb3::compress(cv, m, count, (uint32_t)(rb * 8), flags);
+            vb3::compress(cv, m, a.ctr_base + count, (uint32_t)(rb * 8), flags);
         }
         const bool is_final = count + 1 == a.total_chunks;
         if (!is_final) {
@@ -133,6 +134,51 @@ __global__ void __launch_bounds__(256) k_challenge(const uint8_t* __restrict__ s
     out[i] = vb3::challenge(s, vb3::load_label(label, label_len), label_len, cids ? cids[i] : (uint64_t)i);
 }
 
+// state level -> (ncols, 8 words) rows
+__global__ void __launch_bounds__(128) k_state_level_out(const uint32_t* __restrict__ state, int level,
+                                                         int64_t ncols, uint32_t* __restrict__ out) {
+    const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= ncols) return;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[col * 8 + i] = state[((int64_t)level * 8 + i) * ncols + col];
+}
+
+// Merge sub-tree chaining values into column digests.  The merge order depends only on the block
+// sizes, which are the same for every column, so the host compiles it into a short program:
+// op 0 = push the next block, op 1 = merge the two top entries, op 2 = merge them as the root.
+constexpr int MAX_MERGE_OPS = 192, MAX_MERGE_DEPTH = 48;
+struct MergeArgs {
+    const uint32_t* cvs;   // (nblocks, ncols, 8 words)
+    int64_t ncols;
+    int n_ops;
+    unsigned char ops[MAX_MERGE_OPS];
+    uint32_t* digests;
+};
+__global__ void __launch_bounds__(128) k_merge_subtrees(MergeArgs a) {
+    const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= a.ncols) return;
+    uint32_t st[MAX_MERGE_DEPTH][8];
+    int sp = 0, next = 0;
+    for (int o = 0; o < a.n_ops; ++o) {
+        if (a.ops[o] == 0) {
+            const uint32_t* src = a.cvs + ((int64_t)next * a.ncols + col) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st[sp][i] = __ldg(src + i);
+            ++sp; ++next;
+        } else {
+            uint32_t l[8], r[8], out[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { l[i] = st[sp - 2][i]; r[i] = st[sp - 1][i]; }
+            vb3::parent(l, r, a.ops[o] == 2 ? vb3::ROOT : 0, out);
+            --sp;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st[sp - 1][i] = out[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a.digests[col * 8 + i] = st[0][i];
+}
+
 int state_levels(int64_t total_chunks) {
     int b = 1;
     while ((int64_t(1) << b) < total_chunks) ++b;
@@ -163,12 +209,72 @@ extern "C" int vi_hash_stream_update(void* state, int64_t ncols, int64_t total_r
     StreamArgs a;
     a.rows = rows; a.ncols = ncols; a.n_rows = n_rows;
     a.count0 = (uint64_t)(rows_done / CHUNK_ROWS);
+    a.ctr_base = 0;
     a.total_chunks = total_rows == 0 ? 1 : (uint64_t)((total_rows + CHUNK_ROWS - 1) / CHUNK_ROWS);
     a.state = (uint32_t*)state; a.digests = (uint32_t*)digests;
     const int block = 128;
     vi::ProfScope prof(vi::PROF_HASH, (cudaStream_t)stream);
     k_hash_stream<<<(unsigned)((ncols + block - 1) / block), block, 0, (cudaStream_t)stream>>>(a);
     return vi::check_launch("k_hash_stream");
+}
+
+extern "C" int64_t vi_hash_subtree_state_bytes(int64_t ncols, int level) {
+    if (level < 0 || level > 40) return 0;
+    return vi_hash_stream_state_bytes(ncols, ((int64_t(1) << level) + 1) * CHUNK_ROWS);
+}
+
+extern "C" int vi_hash_subtree(const uint64_t* rows, int64_t n_rows, int64_t ncols, int64_t first_chunk, int level,
+                               void* state, uint8_t* cv_out, void* stream) {
+    VI_REQUIRE(level >= 0 && level <= 40, "hash_subtree: level out of range");
+    VI_REQUIRE(ncols >= 0 && first_chunk >= 0, "hash_subtree: negative size");
+    const int64_t chunks = int64_t(1) << level;
+    VI_REQUIRE(n_rows > (chunks - 1) * CHUNK_ROWS && n_rows <= chunks * CHUNK_ROWS,
+               "hash_subtree: %lld rows are not 2^%d chunks of 128 rows (only the last chunk may be short)",
+               (long long)n_rows, level);
+    VI_REQUIRE(first_chunk % chunks == 0, "hash_subtree: first_chunk must be a multiple of 2^level");
+    if (ncols == 0) return VI_OK;
+    VI_REQUIRE(rows && state && cv_out, "hash_subtree: null pointer");
+    StreamArgs a;
+    a.rows = rows; a.ncols = ncols; a.n_rows = n_rows;
+    a.count0 = 0; a.ctr_base = (uint64_t)first_chunk;
+    a.total_chunks = (uint64_t)chunks + 1;            // never final: no ROOT inside a sub-tree
+    a.state = (uint32_t*)state; a.digests = nullptr;
+    const int block = 128;
+    const unsigned grid = (unsigned)((ncols + block - 1) / block);
+    {
+        vi::ProfScope prof(vi::PROF_HASH, (cudaStream_t)stream);
+        k_hash_stream<<<grid, block, 0, (cudaStream_t)stream>>>(a);
+    }
+    k_state_level_out<<<grid, block, 0, (cudaStream_t)stream>>>((const uint32_t*)state, level, ncols, (uint32_t*)cv_out);
+    return vi::check_launch("k_hash_stream<subtree>");
+}
+
+extern "C" int vi_hash_merge_subtrees(const uint8_t* cvs, const int32_t* levels, int nblocks, int64_t ncols,
+                                      uint8_t* digests, void* stream) {
+    VI_REQUIRE(nblocks >= 2, "hash_merge: at least two sub-trees are needed (a single one would need the root flag inside)");
+    VI_REQUIRE(ncols >= 0 && levels, "hash_merge: bad arguments");
+    MergeArgs a;
+    a.cvs = (const uint32_t*)cvs; a.ncols = ncols; a.digests = (uint32_t*)digests; a.n_ops = 0;
+    // binary-counter merging of equal-sized neighbours, the last block is not merged eagerly,
+    // then a right-to-left fold whose last merge is the root (BLAKE3's incremental tree)
+    int stack[MAX_MERGE_DEPTH], sp = 0;
+    auto emit = [&](unsigned char op) { if (a.n_ops < MAX_MERGE_OPS) a.ops[a.n_ops] = op; ++a.n_ops; };
+    for (int i = 0; i < nblocks; ++i) {
+        VI_REQUIRE(levels[i] >= 0 && levels[i] <= 40, "hash_merge: bad level");
+        VI_REQUIRE(sp == 0 || stack[sp - 1] >= levels[i], "hash_merge: blocks are not a left-to-right decomposition");
+        VI_REQUIRE(sp < MAX_MERGE_DEPTH, "hash_merge: too many pending sub-trees");
+        stack[sp++] = levels[i];
+        emit(0);
+        if (i == nblocks - 1) break;
+        while (sp >= 2 && stack[sp - 1] == stack[sp - 2]) { --sp; ++stack[sp - 1]; emit(1); }
+    }
+    while (sp >= 2) { --sp; emit(sp == 1 ? 2 : 1); }
+    VI_REQUIRE(a.n_ops <= MAX_MERGE_OPS, "hash_merge: merge program too long (%d ops)", a.n_ops);
+    if (ncols == 0) return VI_OK;
+    VI_REQUIRE(cvs && digests, "hash_merge: null pointer");
+    const int block = 128;
+    k_merge_subtrees<<<(unsigned)((ncols + block - 1) / block), block, 0, (cudaStream_t)stream>>>(a);
+    return vi::check_launch("k_merge_subtrees");
 }
 
 extern "C" int64_t vi_hash_columns_scratch_bytes(int64_t m, int64_t ncols) {

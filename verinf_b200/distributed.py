@@ -1,0 +1,198 @@
+"""Multi-GPU sharding of the hot path (one process per GPU, torch.distributed).
+
+The reference is single-GPU; this is the sharding the path admits naturally:
+
+* encode: rows are independent -> contiguous row ranges per rank, no communication;
+* column hash of ONE tree over all rows: every rank reduces the aligned blocks of its row
+  range to non-root BLAKE3 sub-tree chaining values (32 B per column per block), the values
+  are all-gathered and every rank folds them into the leaves, then builds the Merkle tree;
+* sumcheck: rank g holds the entries i = g (mod G) of every table, so each fold stays local;
+  per round the deg+1 partial sums are all-reduced (as 32-bit limbs, summed exactly, then
+  reduced mod p on the host); the last log2 G rounds run on the gathered G-entry tables.
+
+The collectives go through torch.distributed (NCCL on GPUs, gloo in the CPU tests); the
+local compute is injected (`backend`), so the host logic here is testable without a GPU.
+"""
+from typing import Callable, List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+P = (1 << 64) - (1 << 32) + 1
+CHUNK_ROWS = 128
+
+
+def split_rows(total_rows: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous [start, end) row ranges, one per rank, cut on 128-row chunk boundaries and as
+    even as the chunk count allows (trailing ranks may be empty when there are few chunks)."""
+    chunks = max(1, -(-total_rows // CHUNK_ROWS))
+    base, extra = divmod(chunks, world)
+    out, c = [], 0
+    for r in range(world):
+        n = base + (1 if r < extra else 0)
+        out.append((min(c * CHUNK_ROWS, total_rows), min((c + n) * CHUNK_ROWS, total_rows)))
+        c += n
+    return out
+
+
+def aligned_blocks(start_row: int, end_row: int) -> List[Tuple[int, int, int]]:
+    """Greedy decomposition of a chunk-aligned row range into maximal aligned power-of-two chunk
+    blocks: [(first_row, n_rows, level)], block = 2^level chunks starting at a multiple of 2^level."""
+    if start_row >= end_row:
+        return []
+    assert start_row % CHUNK_ROWS == 0
+    c0, c1 = start_row // CHUNK_ROWS, -(-end_row // CHUNK_ROWS)
+    out = []
+    while c0 < c1:
+        lvl = 0
+        while c0 % (2 << lvl) == 0 and c0 + (2 << lvl) <= c1:
+            lvl += 1
+        r0 = c0 * CHUNK_ROWS
+        out.append((r0, min(end_row, (c0 + (1 << lvl)) * CHUNK_ROWS) - r0, lvl))
+        c0 += 1 << lvl
+    return out
+
+
+class CudaBackend:
+    """Local compute on this rank's GPU through the C ABI."""
+
+    def __init__(self, k_deg, n_lig, master_seed=None):
+        from . import cuda_primitives as cp
+        self.cp, self.k, self.n, self.seed = cp, k_deg, n_lig, master_seed
+
+    def encode(self, msg, row_offset):
+        return self.cp.encode_rows(msg, self.k, self.n, master_seed=self.seed, row_offset=row_offset,
+                                   need_polys=False)[1]
+
+    def hash_columns(self, codes):
+        return self.cp.hash_columns_streamed(codes)
+
+    def hash_subtree(self, rows, first_chunk, level):
+        from ._lib import LIB, check, ptr, scratch, stream_ptr
+        n = rows.size(1)
+        out = torch.empty((n, 32), dtype=torch.uint8, device=rows.device)
+        nb = LIB.vi_hash_subtree_state_bytes(n, level)
+        st = scratch(nb, rows.device, "subtree")
+        with torch.cuda.device(rows.device):
+            check(LIB.vi_hash_subtree(ptr(rows), rows.size(0), n, first_chunk, level, ptr(st), ptr(out), stream_ptr()))
+        return out
+
+    def merge(self, cvs, levels):
+        import numpy as np
+        from ._lib import LIB, check, ptr, stream_ptr
+        nb, n, _ = cvs.shape
+        lv = np.asarray(levels, dtype=np.int32)
+        out = torch.empty((n, 32), dtype=torch.uint8, device=cvs.device)
+        with torch.cuda.device(cvs.device):
+            check(LIB.vi_hash_merge_subtrees(ptr(cvs), lv.ctypes.data, nb, n, ptr(out), stream_ptr()))
+        return out
+
+    def merkle(self, leaves):
+        return self.cp.merkle_build_blake3(leaves)
+
+
+def commit_rows_sharded(msg_local, total_rows: int, backend, group=None, row_offset: int = 0):
+    """One commitment over `total_rows` message rows of which this rank holds its split_rows() range.
+
+    Returns (root, levels, codewords_local).  The root equals the single-GPU commit of the
+    concatenated rows: encode locally, hash the local aligned blocks to sub-tree chaining values,
+    all-gather them (32 bytes per column per block), fold and build the Merkle tree on every rank."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    ranges = split_rows(total_rows, world)
+    r0, r1 = ranges[rank]
+    assert msg_local.shape[0] == r1 - r0, f"rank {rank} must hold rows [{r0}, {r1})"
+    codes = backend.encode(msg_local, row_offset + r0)
+    plan = [aligned_blocks(a, b) for a, b in ranges]          # every rank can compute every rank's plan
+    n_blocks = sum(len(p) for p in plan)
+    if n_blocks < 2:                                          # a single sub-tree would need the root flag inside
+        assert world == 1 or all(len(p) == 0 for i, p in enumerate(plan) if i != 0)
+        leaves = backend.hash_columns(codes) if rank == 0 or world == 1 else None
+        if world > 1:
+            box = [leaves]
+            dist.broadcast_object_list(box, src=0, group=group)
+            leaves = box[0]
+        root, levels = backend.merkle(leaves)
+        return root, levels, codes
+    mine = [backend.hash_subtree(codes[b0 - r0:b0 - r0 + cnt], b0 // CHUNK_ROWS, lvl) for b0, cnt, lvl in plan[rank]]
+    width = max(len(p) for p in plan)
+    ncols = codes.shape[1]
+    local = torch.zeros((width, ncols, 32), dtype=torch.uint8, device=codes.device)
+    for i, cv in enumerate(mine):
+        local[i] = cv
+    if world > 1:
+        gathered = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(gathered, local, group=group)
+    else:
+        gathered = [local]
+    cvs = torch.cat([gathered[r][:len(plan[r])] for r in range(world) if len(plan[r])])
+    levels_list = [lvl for p in plan for _, _, lvl in p]
+    leaves = backend.merge(cvs.contiguous(), levels_list)
+    root, levels = backend.merkle(leaves)
+    return root, levels, codes
+
+
+def allreduce_field(values: Sequence[int], device, group=None) -> List[int]:
+    """Exact sum mod p over the ranks of a few field elements.  Collectives have no mod-p sum, so
+    each 64-bit value travels as two 32-bit limbs in int64 lanes (the integer sum of up to 2^31
+    ranks cannot overflow) and is recombined and reduced on the host."""
+    vals = [int(v) % P for v in values]
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return vals
+    limbs = torch.tensor([[v & 0xFFFFFFFF, v >> 32] for v in vals], dtype=torch.int64, device=device)
+    dist.all_reduce(limbs, op=dist.ReduceOp.SUM, group=group)
+    return [(int(lo) + (int(hi) << 32)) % P for lo, hi in limbs.cpu().tolist()]
+
+
+def shard_table(table: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Entries i = rank (mod world) of a 2^n-entry table: with this split the most-significant-first
+    folds of the first n - log2(world) rounds never cross ranks."""
+    return table.view(torch.int64)[..., rank::world].contiguous().view(table.dtype)
+
+
+def prove_terms_sharded(local_problem, make_problem: Callable, coin: Callable[[int], int], n_rounds: int,
+                        device, group=None):
+    """Sumcheck over tables sharded with shard_table().
+
+    local_problem  this rank's shard: object with claim() -> int, round(r or None) -> samples or
+                   None, finals() -> [value per table] (verinf_b200.layergkr_gpu.SumcheckProblem)
+    make_problem   builds the same kind of object from an (n_tables, G) uint64 tensor of gathered
+                   residual entries, for the last log2(G) rounds
+    Returns (claim, round_polys, challenges) identical to the unsharded prover's."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    log_g = world.bit_length() - 1
+    assert 1 << log_g == world, "world size must be a power of two"
+    local_rounds = n_rounds - log_g
+    assert local_rounds >= 0, "tables smaller than the world size"
+    claim = allreduce_field([local_problem.claim()], device, group)[0]
+    polys, chals = [], []
+    r = None
+    for rnd in range(local_rounds):
+        ys = allreduce_field(local_problem.round(r), device, group)
+        polys.append(list(enumerate(ys)))
+        r = coin(rnd) % P
+        chals.append(r)
+    if local_rounds:
+        local_problem.round(r)                    # last local fold: one residual entry per table
+    if log_g == 0:
+        return claim, polys, chals
+    mine = torch.tensor([[v & 0xFFFFFFFF, v >> 32] for v in local_problem.finals()], dtype=torch.int64, device=device)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine, group=group)
+    rows = [[(int(lo) + (int(hi) << 32)) for lo, hi in p.cpu().tolist()] for p in parts]   # [rank][table]
+    n_tables = len(rows[0])
+    tail = torch.tensor([[_as_i64(rows[g][t]) for g in range(world)] for t in range(n_tables)],
+                        dtype=torch.int64, device=device).view(torch.uint64)
+    tail_problem = make_problem(tail)
+    r = None
+    for rnd in range(local_rounds, n_rounds):
+        ys = tail_problem.round(r)
+        polys.append(list(enumerate(ys)))
+        r = coin(rnd) % P
+        chals.append(r)
+    tail_problem.round(r)
+    return claim, polys, chals
+
+
+def _as_i64(v: int) -> int:
+    return v - (1 << 64) if v >= (1 << 63) else v
