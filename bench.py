@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sumcheck", action="store_true", help="also time the 2^24 degree-3 sumcheck")
+    ap.add_argument("--extra", action="store_true",
+                    help="also run the secondary workloads: fused K-quant lift+encode, 7B-layer commit+sumcheck")
     return ap.parse_args()
 
 
@@ -215,7 +217,7 @@ def run_native(a):
     root_hex = bytes(root.cpu().tolist()).hex()
 
     # end to end: pinned host input -> H2D -> commit -> D2H root, all inside the timed region
-    e2e_ms = None
+    e2e_ms, host = None, None
     if not a.no_e2e:
         host = torch.empty((rows, k), dtype=torch.uint64).pin_memory()
         host.copy_(msg)
@@ -237,9 +239,16 @@ def run_native(a):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
 
+    h2d_bytes, d2h_bytes = com.h2d_bytes, com.d2h_bytes
     extra = {}
-    if a.sumcheck and rank == 0:
+    if (a.sumcheck or a.extra) and rank == 0:
         extra["sumcheck"] = time_sumcheck(torch, dev)
+    if a.extra and rank == 0:
+        from verinf_b200 import workloads
+        del com, msg, raw, host
+        torch.cuda.empty_cache()
+        extra["kquant_fused_encode"] = [workloads.kquant_fused_encode(dev, q) for q in ("Q4_K", "Q6_K")]
+        extra["layer7b"] = workloads.layer7b_commit_sumcheck(dev)
 
     if rank == 0:
         elems = world * rows * n
@@ -280,7 +289,7 @@ def run_native(a):
         }
         if e2e_ms:
             line["e2e"] = {"value": elems * a.steps / (e2e_ms * 1e-3), "unit": UNIT,
-                           "h2d_bytes_per_step": com.h2d_bytes, "d2h_bytes_per_step": com.d2h_bytes,
+                           "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                            "ms_per_step": e2e_ms / a.steps}
         if world == 1 and not a.no_cpu:
             crow = a.cpu_rows or auto_cpu_rows(a)

@@ -1,0 +1,150 @@
+"""Synthetic, seeded end-to-end workloads on top of the kernels (shapes of a Llama-2-7B decoder
+layer; no checkpoint is needed).  Used by `bench.py --extra` to report the secondary figures:
+fused K-quant lift + encode of one MLP weight, and commit + sumcheck of a whole layer.
+
+Layout conventions follow the reference: dense row packing of each flattened tensor into message
+rows of ELL slots (prover/core.py:389-458), production geometry ELL=8192, K=16384, N=65536 with the
+row_prg pad (prover/admission.py:43), int8 values lifted with the signed-to-field map
+(prover/loader.py:52-58), one deg-2 sumcheck per matmul over the projected vectors
+(layergkr/full_layer.py:203-230).
+"""
+import time
+
+import numpy as np
+import torch
+
+from . import cuda_primitives as cp
+from . import kquant_cuda as kq
+from . import layergkr_gpu as lg
+from .commit import RowCommitter
+
+P = cp.P
+ELL, K_DEG, N_LIG = 8192, 16384, 65536
+
+
+def _signed_to_field(t_int64):
+    """int64 tensor -> uint64 field tensor, negatives as p - |v| (prover/loader.py:52-58)."""
+    neg = t_int64 < 0
+    out = t_int64.clone()
+    out[neg] = out[neg] + (P - (1 << 64))          # two's complement of p - |v| in int64 lanes
+    return out.view(torch.uint64)
+
+
+def _rand_int8_field(shape, gen, dev):
+    return _signed_to_field(torch.randint(-128, 128, shape, dtype=torch.int64, device=dev, generator=gen))
+
+
+def _pack_rows(flat):
+    """flat field vector -> (rows, ELL) message matrix, zero-filled tail (core.py:389-458)."""
+    n = flat.numel()
+    rows = -(-n // ELL)
+    if rows * ELL == n:
+        return flat.view(torch.int64).reshape(rows, ELL).view(torch.uint64)
+    out = torch.zeros(rows * ELL, dtype=torch.int64, device=flat.device)
+    out[:n] = flat.view(torch.int64).reshape(-1)
+    return out.reshape(rows, ELL).view(torch.uint64)
+
+
+def _timed(fn):
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    r = fn()
+    torch.cuda.synchronize()
+    return r, time.perf_counter() - t0
+
+
+def kquant_fused_encode(dev, qtype="Q4_K", seed=3):
+    """BASELINE config 3: 11008x4096 weight as K-quant super-blocks -> lifted and RS-encoded
+    (transposed view, 5504 rows).  Compares the fused op with lift + transpose + pack + encode."""
+    d_out, d_in = 11008, 4096
+    nb = d_out * d_in // 256
+    rng = np.random.default_rng(seed)
+    raw = rng.integers(0, 256, size=(nb, kq.BLOCK_BYTES[qtype]), dtype=np.uint8)
+    scale = np.clip(rng.normal(0, 0.02, size=(nb, 2)), -6e4, 6e4).astype(np.float16).view(np.uint8).reshape(nb, 4)
+    if qtype == "Q6_K":
+        raw[:, 208:210] = scale[:, :2]
+    else:
+        raw[:, 0:4] = scale
+    raw_t = torch.from_numpy(raw).to(dev)
+    seed_t = torch.arange(32, dtype=torch.uint8, device=dev)
+    S = 1 << 12
+
+    def unfused():
+        w = kq.kquant_to_field(raw_t, qtype, S)
+        wt = w.view(torch.int64).view(d_out, d_in).T.contiguous().view(torch.uint64).reshape(-1)
+        return cp.encode_rows(_pack_rows(wt), K_DEG, N_LIG, master_seed=seed_t, need_polys=False)[1]
+
+    def fused():
+        return kq.kquant_encode_rows(raw_t, qtype, S, d_out, d_in, ell=ELL, k_deg=K_DEG, n_lig=N_LIG,
+                                     transpose=True, master_seed=seed_t)[1]
+
+    a, _ = _timed(unfused)
+    b, _ = _timed(fused)
+    same = bool(torch.equal(a.view(torch.int64), b.view(torch.int64)))
+    del a
+    _, t_unf = _timed(unfused)
+    _, t_fus = _timed(fused)
+    rows = b.size(0)
+    return {"qtype": qtype, "rows": rows, "bit_identical_to_unfused": same, "fused_ms": t_fus * 1e3,
+            "unfused_ms": t_unf * 1e3, "encoded_elems_per_s": rows * N_LIG / t_fus,
+            "codeword_gbs": rows * N_LIG * 8 / t_fus / 1e9}
+
+
+def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
+    """BASELINE config 5 (dense variant): int8 weights/activations of one Llama-2-7B-shaped layer,
+    every weight and activation tensor committed (encode + column hash + Merkle), one deg-2
+    sumcheck per matmul on the projected vectors.  Returns stage seconds."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    d, dff = 4096, 11008
+    shapes = {"W_Q": (d, d), "W_K": (d, d), "W_V": (d, d), "W_O": (d, d), "W_gate": (d, dff), "W_up": (d, dff),
+              "W_down": (dff, d)}
+    W = {k: _rand_int8_field(s, g, dev) for k, s in shapes.items()}
+    X = {k: _rand_int8_field((seq, s[0]), g, dev) for k, s in shapes.items()}      # input of each matmul
+    (Y, t_mm) = _timed(lambda: {k: cp.gl_matmul(X[k], W[k]) for k in shapes})
+    seed_t = torch.arange(32, dtype=torch.uint8, device=dev)
+    committers = {}
+
+    def commit(t, row_off):
+        msg = _pack_rows(t.reshape(-1))
+        c = committers.get(msg.size(0))
+        if c is None:
+            c = committers[msg.size(0)] = RowCommitter(msg.size(0), ELL, K_DEG, N_LIG, master_seed=seed_t, device=dev)
+        return bytes(c.commit(msg.contiguous(), row_offset=row_off).cpu().tolist()), msg.size(0)
+
+    def commit_all():
+        roots, rows, off = {}, 0, 0
+        for name, t in list(W.items()) + [("X_" + k, v) for k, v in X.items()] + [("Y_" + k, v) for k, v in Y.items()]:
+            roots[name], r = commit(t, off)
+            rows += r
+            off += r
+        return roots, rows
+
+    commit_all()                                                  # warm-up (tables, allocator)
+    (roots, n_rows), t_commit = _timed(commit_all)
+
+    def sumchecks():
+        ok = True
+        for name in shapes:
+            n_in, n_out = shapes[name]
+            rho = _rand_int8_field((seq,), g, dev)
+            tau = _rand_int8_field((n_out,), g, dev)
+            a = cp.gl_matvec(X[name].view(torch.int64).T.contiguous().view(torch.uint64), rho)      # X^T rho  (n_in)
+            b = cp.gl_matvec(W[name], tau)                                                            # W tau    (n_in)
+            width = 1 << (n_in - 1).bit_length()
+            fa = torch.zeros(width, dtype=torch.int64, device=dev); fa[:n_in] = a.view(torch.int64)
+            fb = torch.zeros(width, dtype=torch.int64, device=dev); fb[:n_in] = b.view(torch.int64)
+            coins = [((i + 1) * 0x9E3779B97F4A7C15 + 7) % P for i in range(width.bit_length() - 1)]
+            claim, polys, _, _ = lg.prove_terms_gpu([(1, [fa.view(torch.uint64), fb.view(torch.uint64)])],
+                                                    lambda i: coins[i])
+            yt = cp.gl_matvec(Y[name], tau)                                                           # Y tau (seq)
+            want = int(cp.gl_matvec(yt.reshape(1, -1), rho)[0].item())                                # rho^T Y tau
+            ok = ok and claim == want and (polys[0][0][1] + polys[0][1][1]) % P == claim
+        return ok
+
+    sumchecks()
+    ok, t_sc = _timed(sumchecks)
+    return {"seq": seq, "rows_committed": n_rows, "codeword_gb": n_rows * N_LIG * 8 / 1e9,
+            "commit_s": t_commit, "sumcheck_s": t_sc, "commit_plus_sumcheck_s": t_commit + t_sc,
+            "witness_matmul_s": t_mm, "sumcheck_claims_match_rho_Y_tau": bool(ok),
+            "root_W_Q": roots["W_Q"].hex()}
