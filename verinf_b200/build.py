@@ -35,9 +35,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     env = dict(os.environ)
     env.pop("CC", None)
     env.pop("CXX", None)
+    extra = os.environ.get("VERINF_NVCC_EXTRA", "").split()      # experiment switches, e.g. -DVGL_SHIFT_ALU
     for src in SOURCES:
         obj = CSRC / (src[:-3] + ".o")
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

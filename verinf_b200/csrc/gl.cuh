@@ -154,15 +154,9 @@ __device__ __forceinline__ uint64_t pow(uint64_t base, uint64_t e) {
 //   S <  32: (l1:l0) + l2*(2^32-1)
 //   S <  64: the general 128-bit reduction of (l2:l1:l0:0)
 //   S >= 64: l0*(2^32-1) - (l2:l1)
-// 2^v for v < 32 read from the constant bank: a multiplier the assembler cannot fold, so the
-// limb shifts below are issued as wide multiply-adds on the FMA pipe instead of funnel shifts on
-// the (saturated) ALU pipe.
-static __constant__ uint32_t POW2_TAB[32] = {
-    1u << 0,  1u << 1,  1u << 2,  1u << 3,  1u << 4,  1u << 5,  1u << 6,  1u << 7,
-    1u << 8,  1u << 9,  1u << 10, 1u << 11, 1u << 12, 1u << 13, 1u << 14, 1u << 15,
-    1u << 16, 1u << 17, 1u << 18, 1u << 19, 1u << 20, 1u << 21, 1u << 22, 1u << 23,
-    1u << 24, 1u << 25, 1u << 26, 1u << 27, 1u << 28, 1u << 29, 1u << 30, 1u << 31};
-
+// (Issuing the limb shifts as wide multiplies on the FMA pipe, or building the 64-bit sums from
+// mad.wide plus a 64-bit compare instead of carry chains, was measured slower on B200: see
+// profiles/int_pipes_sm100a.md.)
 template <int S>
 __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
     static_assert(S >= 0 && S < 96, "shift out of range");
@@ -174,11 +168,7 @@ __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
         // (l2:l1:l0) = x << V as three 32-bit limbs
         uint32_t l0 = (uint32_t)x, l1 = (uint32_t)(x >> 32), l2 = 0;
         if constexpr (V != 0) {
-            const uint32_t c = POW2_TAB[V];
-            uint64_t t, u;
-            asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(l0), "r"(c));
-            asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(u) : "r"(l1), "r"(c), "l"(t >> 32));
-            l0 = (uint32_t)t; l1 = (uint32_t)u; l2 = (uint32_t)(u >> 32);
+            l2 = l1 >> (32 - V); l1 = (l1 << V) | (l0 >> (32 - V)); l0 <<= V;
         }
         if constexpr (U == 0) {
             // l0 + l1 phi + l2 phi^2 = (l1:l0) + l2*(2^32-1)

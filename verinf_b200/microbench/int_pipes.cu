@@ -67,6 +67,40 @@ __global__ void __launch_bounds__(BLOCK) k_field(uint64_t* out, uint64_t seed) {
     out[blockIdx.x * BLOCK + threadIdx.x] = acc;
 }
 
+
+// ---- self-check of the device field primitives against 128-bit integer arithmetic ----------
+template <int S> __device__ bool chk_pow2(uint64_t x) {
+    unsigned __int128 v = (unsigned __int128)x;
+    for (int i = 0; i < S; ++i) { v <<= 1; if (v >= vgl::P) v -= vgl::P; }
+    return vgl::mul_pow2<S>(x) == (uint64_t)v;
+}
+__device__ uint64_t edge_or_rand(uint64_t i, uint64_t salt) {
+    const uint64_t P = vgl::P;
+    const uint64_t edges[12] = {0, 1, 2, P - 1, P - 2, 0xFFFFFFFFull, 0x100000000ull, 0xFFFFFFFF00000000ull,
+                                0x8000000000000000ull, 0xFFFFFFFEFFFFFFFFull, 0x00000000FFFFFFFEull, P - 0xFFFFFFFFull};
+    if ((i & 7) == 0) return edges[(i >> 3) % 12];
+    uint64_t z = (i + salt) * 0x9E3779B97F4A7C15ull; z ^= z >> 31; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 29;
+    return z % P;
+}
+__global__ void k_selfcheck(unsigned long long* bad) {
+    using namespace vgl;
+    uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    uint64_t a = edge_or_rand(i, 1), b = edge_or_rand(i / 3 + (i & 7) * 11, 7);
+    unsigned __int128 A = a, B = b;
+    int f = 0;
+    if (add(a, b) != (uint64_t)((A + B) % P)) f |= 1;
+    if (sub(a, b) != (uint64_t)((A + P - B) % P)) f |= 2;
+    if (mul(a, b) != (uint64_t)((A * B) % P)) f |= 4;
+    uint64_t hi = edge_or_rand(i * 5 + 3, 99) | (i & 1 ? 0xFFFFFFFF00000000ull : 0), lo = a | (i & 2 ? 0xFFFFFFFF00000000ull : 0);
+    unsigned __int128 W = ((unsigned __int128)hi << 64) | lo;
+    if (reduce128(lo, hi) != (uint64_t)(W % P)) f |= 8;
+    if (sub(a, P) != a) f |= 16;
+    if (!(chk_pow2<1>(a) && chk_pow2<12>(a) && chk_pow2<24>(a) && chk_pow2<31>(a) && chk_pow2<32>(a) && chk_pow2<36>(a) &&
+          chk_pow2<48>(a) && chk_pow2<60>(a) && chk_pow2<63>(a) && chk_pow2<64>(a) && chk_pow2<72>(a) && chk_pow2<84>(a) &&
+          chk_pow2<95>(a))) f |= 32;
+    if (f) atomicOr(bad, (unsigned long long)f);
+}
+
 template <class F>
 float time_ms(F launch) {
     cudaEvent_t a, b;
@@ -82,6 +116,14 @@ float time_ms(F launch) {
 int main() {
     void* d = nullptr;
     if (cudaMalloc(&d, (size_t)GRID * BLOCK * 8) != cudaSuccess) { printf("no CUDA device\n"); return 1; }
+    {
+        unsigned long long* bad; cudaMalloc(&bad, 8); cudaMemset(bad, 0, 8);
+        k_selfcheck<<<4096, 256>>>(bad);
+        unsigned long long h = 0; cudaMemcpy(&h, bad, 8, cudaMemcpyDeviceToHost);
+        printf("self-check of add/sub/mul/reduce128/mul_pow2 vs 128-bit arithmetic: %s (flags %llu) %s\n",
+               h ? "MISMATCH" : "ok", h, cudaGetErrorString(cudaGetLastError()));
+        cudaFree(bad);
+    }
     int khz = 0; cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, 0);
     const double threads = (double)GRID * BLOCK;
     auto raw = [&](const char* name, int per, float ms) {
