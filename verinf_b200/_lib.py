@@ -4,12 +4,13 @@ The library is the only compute path: if it is missing or fails to load, importi
 this module raises — there is no CPU or PyTorch fallback.
 """
 import ctypes as C
+import os
 from pathlib import Path
 
 import torch
 
 _HERE = Path(__file__).resolve().parent
-SO_PATH = _HERE / "libverinf_b200.so"
+SO_PATH = Path(os.environ.get("VERINF_LIB") or _HERE / "libverinf_b200.so")   # VERINF_LIB: build under test
 
 _i64, _u64, _int, _p, _dbl = C.c_int64, C.c_uint64, C.c_int, C.c_void_p, C.c_double
 

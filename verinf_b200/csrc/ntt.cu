@@ -154,8 +154,21 @@ struct PassArgs {
     int64_t kq_dout, kq_din, kq_first_row;
 };
 
-template <int LOGL, bool INV, int MODE>   // MODE 0: input contiguous along columns; 1: along the DFT index
-__global__ void __launch_bounds__(512) k_pass(PassArgs a) {
+// Minimum resident CTAs per SM asked of the compiler for the 256-thread tiles (register budget =
+// 65536 / (256 * blocks)).  Measured on B200 at K = 2^16: k_pass 1/3/4/5/6/8 blocks -> commit
+// 32.6 / 30.2 / 27.5 / 27.3 / 28.5 / 32.0 ms; k_encode_mid is best at 2 (128 registers).
+#ifndef VI_PASS_MINB
+#define VI_PASS_MINB 5
+#endif
+#ifndef VI_MID_MINB
+#define VI_MID_MINB 2
+#endif
+// MODE 0: input contiguous along columns; 1: along the DFT index
+// tiles of DFT length 2^4..2^8 always run 256 threads (4096 elements / 16 per thread)
+__host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4 && logl <= 8) ? 256 : 512; }
+
+template <int LOGL, bool INV, int MODE>
+__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? VI_PASS_MINB : 1) k_pass(PassArgs a) {
     using SC = Sched<LOGL, false>;
     constexpr int L = 1 << LOGL, EPT = SC::EPT;
     extern __shared__ uint64_t sm[];
@@ -264,7 +277,7 @@ struct MidArgs {
 };
 
 template <int LOGL>
-__global__ void __launch_bounds__(512) k_encode_mid(MidArgs a) {
+__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? VI_MID_MINB : 1) k_encode_mid(MidArgs a) {
     using SI = Sched<LOGL, false>;   // inverse: small stage first, radix-16 last
     using SF = Sched<LOGL, true>;    // forward: radix-16 first, small stage last
     constexpr int L = 1 << LOGL, EPT = SI::EPT;
