@@ -258,6 +258,10 @@ def run_native(a):
         dom = max(prof.items(), key=lambda kv: kv[1][0])
         per_row = {"encode_pass1": 8 * (k + k), "encode_mid": 8 * (k + n), "encode_pass3": 8 * (n + n),
                    "hash_columns": 8 * n}
+        # DRAM bytes per message row from the committed ncu captures (profiles/*.md: dram read + write of
+        # one launch / rows of that launch), valid for this geometry only; scaled to an average launch
+        ncu_per_row = {"encode_pass1": 1.597e6, "encode_mid": 2.515e6, "encode_pass3": 4.343e6,
+                       "hash_columns": 2.197e6} if (a.log_k, a.blowup) == (16, 4) else {}
         launches = sum(v[1] for v in prof.values())
         bytes_per_step = rows * per_row.get(dom[0], 0)
         dom_ms_per_step = dom[1][0] / a.steps
@@ -273,7 +277,8 @@ def run_native(a):
                        "root": root_hex},
             "roofline": {"bound": "hbm", "kernel": dom[0], "achieved": achieved, "peak": hbm_peak,
                          "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
-                         "traffic": None, "launches_per_step": dom[1][1] / a.steps,
+                         "traffic": (ncu_per_row[dom[0]] * rows * a.steps / dom[1][1]) if dom[0] in ncu_per_row else None,
+                         "launches_per_step": dom[1][1] / a.steps,
                          "ms_per_launch": dom[1][0] / dom[1][1],
                          "algorithmic_bytes_per_step": bytes_per_step,
                          "share_of_device_time": dom[1][0] / total_prof},
