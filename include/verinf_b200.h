@@ -179,6 +179,12 @@ int64_t vi_sumcheck_scratch_bytes(void);
 int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                       int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
                       uint64_t* out, void* partials, void* stream);
+/* All rounds for challenges known up front (HOST array coins[n_rounds], size = 2^n_rounds): queues
+ * every fold+evaluate launch without a host round trip; samples (device, n_rounds x 8 u64) receives
+ * g(0..deg) of round i at samples[8*i ..].  Equivalent to n_rounds + 1 calls of vi_sumcheck_round. */
+int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
+                    int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
+                    const uint64_t* coins, int n_rounds, uint64_t* samples, void* partials, void* stream);
 int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                       int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
                       int fold, uint64_t r, uint64_t* out, void* partials, void* stream);

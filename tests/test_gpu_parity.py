@@ -437,6 +437,10 @@ def test_sumcheck_vs_oracle(logn, terms):
         r = coins[rnd]
     assert prob.round(r) is None
     assert prob.finals() == [int(v) for v in finals]
+    prob2 = lg.SumcheckProblem(dev(tabs), terms)          # all rounds queued at once, coins known up front
+    got = prob2.run(coins)
+    assert got == [[int(v) for v in row[:len(got[0])]] for row in samples]
+    assert prob2.finals() == [int(v) for v in finals]
 
 
 # ---------------------------------------------------------------- misc ops ---

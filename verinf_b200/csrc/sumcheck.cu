@@ -253,3 +253,21 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
     k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
     return vi::check_launch("k_sumcheck<fold+round>");
 }
+
+extern "C" int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
+                               int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
+                               const uint64_t* coins, int n_rounds, uint64_t* samples, void* partials, void* stream) {
+    VI_REQUIRE(vi::is_pow2(size) && (int64_t(1) << n_rounds) == size, "sumcheck_run: size must be 2^n_rounds");
+    VI_REQUIRE(n_rounds == 0 || (coins && samples), "sumcheck_run: null pointer");
+    int64_t cur = size;
+    for (int rnd = 0; rnd < n_rounds; ++rnd) {
+        int rc = vi_sumcheck_round(tables, stride, n_tables, cur, n_terms, coefs, nfac, fac, rnd > 0,
+                                   rnd > 0 ? coins[rnd - 1] : 0, samples + (int64_t)rnd * 8, partials, stream);
+        if (rc) return rc;
+        if (rnd > 0) cur /= 2;
+    }
+    if (n_rounds)   // last fold: every table collapses to its value at the challenge point
+        return vi_sumcheck_round(tables, stride, n_tables, cur, n_terms, coefs, nfac, fac, 1, coins[n_rounds - 1],
+                                 samples, partials, stream);
+    return VI_OK;
+}

@@ -88,6 +88,21 @@ class SumcheckProblem:
             return None
         return self._read(self.deg + 1)
 
+    def run(self, coins: Sequence[int]):
+        """All rounds back to back for challenges known up front (every call site of the reference
+        pre-draws its coins from the transcript before the sumcheck starts): no host round trip per
+        round, one D2H copy of all samples at the end.  Returns [[g(0..deg)] per round]."""
+        n_rounds = self.size.bit_length() - 1
+        assert len(coins) == n_rounds
+        buf = torch.empty((max(n_rounds, 1), 8), dtype=torch.uint64, device=self.tables.device)
+        cs = np.array([int(c) % P for c in coins], dtype=np.uint64)
+        with torch.cuda.device(self.tables.device):
+            check(LIB.vi_sumcheck_run(ptr(self.tables), *self._args(), cs.ctypes.data, n_rounds, ptr(buf),
+                                      ptr(self._partials), stream_ptr()))
+        self.size = 1
+        host = buf.view(torch.int64).cpu().view(torch.uint64)
+        return [[int(v) for v in row[:self.deg + 1].tolist()] for row in host[:n_rounds]]
+
     def finals(self) -> List[int]:
         return [int(v) for v in self.tables[:, 0].cpu().tolist()]
 
@@ -99,12 +114,15 @@ def _poly_eval(coeffs, x, p):
     return acc
 
 
-def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=None, mu0: int = 0):
+def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=None, mu0: int = 0,
+                    coins: Optional[Sequence[int]] = None):
     """Sumcheck prover for sum_x sum_k c_k prod_j f_kj(x): returns
     (claim, round_polys [[(x, y), ...] per round], challenges, final_mask).
 
     `terms` is [(coef, [factor, ...])] where a factor is a Python sequence or a 1-D uint64
-    CUDA tensor; factors that are the same object share one device table."""
+    CUDA tensor; factors that are the same object share one device table.  When the challenges are
+    known up front pass them as `coins` (then `coin` is not called): all rounds are queued without a
+    host round trip."""
     assert field_p == P
     uniq, index, plan = [], {}, []
     for c, fs in terms:
@@ -129,6 +147,10 @@ def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=No
     mu = mu0 % P
     claim = (prob.claim() + mu) % P
     round_polys, challenges = [], []
+    if coins is not None and mask is None:
+        challenges = [int(c) % P for c in coins]
+        round_polys = [list(enumerate(ys)) for ys in prob.run(challenges)]
+        return claim, round_polys, challenges, mu
     r = None
     for rnd in range(n_rounds):
         ys = prob.round(r)
