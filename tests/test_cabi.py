@@ -40,7 +40,9 @@ def test_size_helpers(lib):
     assert L.vi_hash_stream_state_bytes(100, 64) == 2 * 32 * 100          # one chunk: levels 0..1
     assert L.vi_hash_stream_state_bytes(100, 4096) == 6 * 32 * 100        # 32 chunks: levels 0..5
     assert L.vi_hash_stream_state_bytes(100, 4097) == 7 * 32 * 100
-    assert L.vi_hash_columns_scratch_bytes(4096, 100) == L.vi_hash_stream_state_bytes(100, 4096)
+    assert L.vi_hash_columns_scratch_bytes(4096, 200000) == L.vi_hash_stream_state_bytes(200000, 4096)
+    assert L.vi_hash_columns_scratch_bytes(4096, 100) > L.vi_hash_stream_state_bytes(100, 4096)   # row segments
+    assert L.vi_hash_columns_scratch_bytes(100, 100) == L.vi_hash_stream_state_bytes(100, 100)
     assert L.vi_sumcheck_scratch_bytes() > 0
     assert L.vi_profile_num_tags() >= 9
     assert L.vi_profile_tag_name(0) == b"encode_pass1"
@@ -71,7 +73,7 @@ def test_argument_validation_without_gpu(lib):
     assert L.vi_hash_stream_update(p, 8, 256, 100, p, 128, p, None) != 0 and "multiple of 128" in _err(lib)
     assert L.vi_hash_stream_update(p, 8, 256, 0, p, 100, p, None) != 0 and "partial" in _err(lib)
     assert L.vi_hash_stream_update(p, 8, 256, 128, p, 256, p, None) != 0
-    assert L.vi_hash_columns(p, 4096, 8, p, None, 0, None) != 0 and "scratch" in _err(lib)
+    assert L.vi_hash_columns(p, 4096, 200000, p, None, 0, None) != 0 and "scratch" in _err(lib)
     assert L.vi_challenge(p, p, 9, None, 4, p, None) != 0 and "label" in _err(lib)
     coefs = (C.c_uint64 * 1)(1)
     nfac = (C.c_int32 * 1)(5)

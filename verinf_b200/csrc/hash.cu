@@ -10,6 +10,7 @@
 // size instead of by a stack pointer: level b holds the chaining value of a
 // complete subtree of 2^b chunks (the binary-counter form of BLAKE3's incremental
 // tree), stored [level][word][column] so every access is coalesced.
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/verinf_b200.h"
@@ -30,13 +31,24 @@ struct StreamArgs {
     uint64_t total_chunks;  // chunks of the whole stream (>= 1)
     uint32_t* state;        // [level][8][ncols]
     uint32_t* digests;      // (ncols, 8) words; written by the call that ends the stream
+    // segmented mode (gridDim.y > 1): segment y hashes rows [y*seg_rows, ...) as its own non-final
+    // stream with chunk counters offset by y*seg_rows/128 and its own state block
+    int64_t seg_rows;       // rows per segment (multiple of 128), 0 = not segmented
+    int64_t seg_state;      // uint32 words of state per segment
 };
 
 __global__ void __launch_bounds__(128) k_hash_stream(StreamArgs a) {
     const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= a.ncols) return;
-    const uint64_t* p = a.rows + col;
     const int64_t ld = a.ncols;
+    if (a.seg_rows) {        // this CTA row works on one segment
+        const int64_t seg = blockIdx.y;
+        a.rows += seg * a.seg_rows * ld;
+        a.n_rows = a.n_rows - seg * a.seg_rows < a.seg_rows ? a.n_rows - seg * a.seg_rows : a.seg_rows;
+        a.ctr_base += (uint64_t)(seg * (a.seg_rows / CHUNK_ROWS));
+        a.state += seg * a.seg_state;
+    }
+    const uint64_t* p = a.rows + col;
     const int64_t n_chunks = a.n_rows == 0 ? 1 : (a.n_rows + CHUNK_ROWS - 1) / CHUNK_ROWS;
     const bool single = a.total_chunks == 1;
 
@@ -179,6 +191,25 @@ __global__ void __launch_bounds__(128) k_merge_subtrees(MergeArgs a) {
     for (int i = 0; i < 8; ++i) a.digests[col * 8 + i] = st[0][i];
 }
 
+// gather the sub-tree values a segmented run left in the per-segment states into (nblocks, ncols, 8)
+constexpr int MAX_SEG_BLOCKS = 96;
+struct GatherArgs {
+    const uint32_t* state;
+    int64_t seg_state, ncols;
+    int nblocks;
+    unsigned char seg[MAX_SEG_BLOCKS], level[MAX_SEG_BLOCKS];
+    uint32_t* cvs;
+};
+__global__ void __launch_bounds__(128) k_gather_blocks(GatherArgs a) {
+    const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (col >= a.ncols) return;
+    const uint32_t* st = a.state + (int64_t)a.seg[b] * a.seg_state + (int64_t)a.level[b] * 8 * a.ncols + col;
+    uint32_t* dst = a.cvs + ((int64_t)b * a.ncols + col) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[i] = st[(int64_t)i * a.ncols];
+}
+
 int state_levels(int64_t total_chunks) {
     int b = 1;
     while ((int64_t(1) << b) < total_chunks) ++b;
@@ -209,7 +240,7 @@ extern "C" int vi_hash_stream_update(void* state, int64_t ncols, int64_t total_r
     StreamArgs a;
     a.rows = rows; a.ncols = ncols; a.n_rows = n_rows;
     a.count0 = (uint64_t)(rows_done / CHUNK_ROWS);
-    a.ctr_base = 0;
+    a.ctr_base = 0; a.seg_rows = 0; a.seg_state = 0;
     a.total_chunks = total_rows == 0 ? 1 : (uint64_t)((total_rows + CHUNK_ROWS - 1) / CHUNK_ROWS);
     a.state = (uint32_t*)state; a.digests = (uint32_t*)digests;
     const int block = 128;
@@ -238,7 +269,7 @@ extern "C" int vi_hash_subtree(const uint64_t* rows, int64_t n_rows, int64_t nco
     a.rows = rows; a.ncols = ncols; a.n_rows = n_rows;
     a.count0 = 0; a.ctr_base = (uint64_t)first_chunk;
     a.total_chunks = (uint64_t)chunks + 1;            // never final: no ROOT inside a sub-tree
-    a.state = (uint32_t*)state; a.digests = nullptr;
+    a.state = (uint32_t*)state; a.digests = nullptr; a.seg_rows = 0; a.seg_state = 0;
     const int block = 128;
     const unsigned grid = (unsigned)((ncols + block - 1) / block);
     {
@@ -277,7 +308,36 @@ extern "C" int vi_hash_merge_subtrees(const uint8_t* cvs, const int32_t* levels,
     return vi::check_launch("k_merge_subtrees");
 }
 
+namespace {
+// Row segmentation of a one-shot column hash: with few columns one thread per column leaves the
+// GPU empty, so the rows are cut into up to 64 segments of 2^seg_level chunks that are hashed
+// concurrently (grid.y) to sub-tree values and then folded.  seg_level < 0: not worth it.
+struct SegPlan { int seg_level; int64_t nseg, seg_rows, seg_state_words, state_bytes, cvs_bytes; int nblocks; };
+SegPlan seg_plan(int64_t m, int64_t ncols) {
+    SegPlan p{-1, 0, 0, 0, 0, 0, 0};
+    const int64_t chunks = (m + CHUNK_ROWS - 1) / CHUNK_ROWS;
+    const char* off = getenv("VERINF_HASH_SEGMENTS");
+    if ((off && off[0] == '0') || ncols <= 0 || ncols >= 131072 || chunks < 4) return p;
+    int64_t want = (262144 + ncols - 1) / ncols;            // segments that would fill the GPU
+    if (want > 64) want = 64;
+    int lvl = 0;
+    while ((chunks >> (lvl + 1)) >= want) ++lvl;             // largest 2^lvl with chunks / 2^lvl >= want
+    int64_t nseg = (chunks + (int64_t(1) << lvl) - 1) >> lvl;
+    while (nseg > 64) { ++lvl; nseg = (chunks + (int64_t(1) << lvl) - 1) >> lvl; }
+    if (nseg < 2) return p;
+    p.seg_level = lvl; p.nseg = nseg; p.seg_rows = (int64_t(1) << lvl) * CHUNK_ROWS;
+    p.seg_state_words = (int64_t)(lvl + 2) * 8 * ncols;
+    p.state_bytes = p.seg_state_words * 4 * nseg;
+    const int64_t tail = chunks - (nseg - 1) * (int64_t(1) << lvl);      // chunks of the last segment
+    p.nblocks = (int)(nseg - 1) + __builtin_popcountll((unsigned long long)tail);
+    p.cvs_bytes = (int64_t)p.nblocks * ncols * 32;
+    return p;
+}
+}  // namespace
+
 extern "C" int64_t vi_hash_columns_scratch_bytes(int64_t m, int64_t ncols) {
+    SegPlan p = seg_plan(m, ncols);
+    if (p.seg_level >= 0) return p.state_bytes + p.cvs_bytes;
     return vi_hash_stream_state_bytes(ncols, m);
 }
 
@@ -285,6 +345,43 @@ extern "C" int vi_hash_columns(const uint64_t* mat, int64_t m, int64_t ncols, ui
                                void* scratch, int64_t scratch_bytes, void* stream) {
     VI_REQUIRE(m >= 0 && ncols >= 0, "hash_columns: negative size");
     if (ncols == 0) return VI_OK;
+    const SegPlan sp = seg_plan(m, ncols);
+    if (sp.seg_level >= 0 && scratch != nullptr && scratch_bytes >= sp.state_bytes + sp.cvs_bytes) {
+        cudaStream_t st = (cudaStream_t)stream;
+        VI_REQUIRE(mat && digests, "hash_columns: null pointer");
+        StreamArgs a;
+        a.rows = mat; a.ncols = ncols; a.n_rows = m; a.count0 = 0; a.ctr_base = 0;
+        a.total_chunks = (uint64_t(1) << sp.seg_level) + 1;          // segments never close the tree
+        a.state = (uint32_t*)scratch; a.digests = nullptr;
+        a.seg_rows = sp.seg_rows; a.seg_state = sp.seg_state_words;
+        const int block = 128;
+        dim3 grid((unsigned)((ncols + block - 1) / block), (unsigned)sp.nseg);
+        {
+            vi::ProfScope prof(vi::PROF_HASH, st);
+            k_hash_stream<<<grid, block, 0, st>>>(a);
+        }
+        // blocks left to right: full segments at seg_level, then the binary decomposition of the tail
+        GatherArgs g;
+        int32_t levels[MAX_SEG_BLOCKS];
+        g.state = (const uint32_t*)scratch; g.seg_state = sp.seg_state_words; g.ncols = ncols; g.nblocks = 0;
+        g.cvs = (uint32_t*)((char*)scratch + sp.state_bytes);
+        const int64_t chunks = (m + CHUNK_ROWS - 1) / CHUNK_ROWS;
+        const int64_t tail = chunks - (sp.nseg - 1) * (int64_t(1) << sp.seg_level);
+        for (int64_t sgi = 0; sgi < sp.nseg - 1; ++sgi) {
+            g.seg[g.nblocks] = (unsigned char)sgi; g.level[g.nblocks] = (unsigned char)sp.seg_level;
+            levels[g.nblocks++] = sp.seg_level;
+        }
+        for (int b = 40; b >= 0; --b)
+            if ((tail >> b) & 1) {
+                g.seg[g.nblocks] = (unsigned char)(sp.nseg - 1); g.level[g.nblocks] = (unsigned char)b;
+                levels[g.nblocks++] = b;
+            }
+        dim3 ggrid(grid.x, (unsigned)g.nblocks);
+        k_gather_blocks<<<ggrid, block, 0, st>>>(g);
+        int rc = vi::check_launch("k_hash_stream<segments>");
+        if (rc) return rc;
+        return vi_hash_merge_subtrees((const uint8_t*)g.cvs, levels, g.nblocks, ncols, digests, stream);
+    }
     int64_t need = vi_hash_stream_state_bytes(ncols, m);
     if (m > CHUNK_ROWS && (scratch == nullptr || scratch_bytes < need))
         return vi::fail(VI_ERR_SCRATCH, "hash_columns: scratch of %lld bytes required", (long long)need);
