@@ -171,6 +171,8 @@ def run_native(a):
         raise SystemExit("bench.py: no CUDA device; the native arm has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    from verinf_b200.distributed import bind_to_gpu_numa
+    numa_bound = bind_to_gpu_numa(local)          # pinned host rows next to the GPU that reads them
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -274,6 +276,7 @@ def run_native(a):
             "data": "synthetic",
             "config": {"workload": workload_name(a), "rows_per_gpu": rows, "K": k, "N": n,
                        "l2_policy": "inputs (2 GiB) and outputs (8 GiB) exceed L2; no flush needed",
+                       "numa_bound": numa_bound,
                        "root": root_hex},
             "roofline": {"bound": "hbm", "kernel": dom[0], "achieved": achieved, "peak": hbm_peak,
                          "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,

@@ -196,3 +196,30 @@ def prove_terms_sharded(local_problem, make_problem: Callable, coin: Callable[[i
 
 def _as_i64(v: int) -> int:
     return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def bind_to_gpu_numa(device_index: int) -> bool:
+    """Pin this process to the CPUs NVML reports as local to the GPU, so that pinned host buffers
+    allocated afterwards (first touch) sit on the GPU's NUMA node.  With one rank per GPU feeding
+    gigabytes per step over PCIe this keeps the copies off the inter-socket link.  Only reads
+    device properties; returns False (and changes nothing) if anything is unavailable."""
+    import os
+    try:
+        import pynvml
+        p = torch.cuda.get_device_properties(device_index)
+        pynvml.nvmlInit()
+        try:
+            bus = f"{p.pci_domain_id:08x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(p.uuid)).encode())
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cpus = {64 * w + b for w, m in enumerate(words) for b in range(64) if (int(m) >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if not cpus:
+            return False
+        os.sched_setaffinity(0, cpus)
+        return True
+    except Exception:
+        return False
