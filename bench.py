@@ -269,6 +269,15 @@ def run_native(a):
         dom_ms_per_step = dom[1][0] / a.steps
         achieved = bytes_per_step / (dom_ms_per_step * 1e-3) / 1e9 if dom_ms_per_step else 0.0
         enc_ms = sum(prof.get(t_, (0, 0))[0] for t_ in ("encode_pass1", "encode_mid", "encode_pass3")) / a.steps
+        # integer roofline of the encode: radix-16 butterfly element-stages and full modular multiplies at
+        # their measured ALU-pipe cost (profiles/int_pipes_sm100a.md: 8.8 and 17.3 ALU lane-ops), against
+        # 148 SMs x 64 ALU lanes per clock at the SM clock sampled during the run
+        log_n = a.log_k
+        stages_per_row = (1 + a.blowup) * k * log_n
+        muls_per_row = (1 + a.blowup) * k * 3 + a.blowup * k + k
+        alu_ops = rows * (stages_per_row * 8.8 + muls_per_row * 17.3)
+        sm_hz = ((clocks or {}).get("sm_mhz") or 1965.0) * 1e6
+        alu_floor_ms = alu_ops / (148 * 64 * sm_hz) * 1e3
         line = {
             "metric": METRIC, "value": elems * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps,
@@ -292,6 +301,8 @@ def run_native(a):
             "encode_only": {"ms_per_step": enc_ms,
                             "gbs_algorithmic": rows * 8 * (k + n) / (enc_ms * 1e-3) / 1e9 if enc_ms else None,
                             "frac_of_hbm": rows * 8 * (k + n) / (enc_ms * 1e-3) / 1e9 / hbm_peak if enc_ms else None},
+            "int_roofline": {"bound": "integer ALU pipe (64 lanes/clk/SM)", "encode_floor_ms": alu_floor_ms,
+                             "encode_ms": enc_ms, "frac": alu_floor_ms / enc_ms if enc_ms else None},
             "gpu_launches": launches,
             "clocks": clocks,
         }
