@@ -152,7 +152,8 @@ int vi_kquant_to_field(const uint8_t* raw, int64_t n_blocks, int qtype, double S
  * lifted inside the encode's first pass, so lifted weights never reach HBM.
  * Message slot c of row r is flat element f = (first_row + r)*ell + c of the lifted
  * matrix, transposed (f = k_in*d_out + n_out) when transpose != 0; slots past the end
- * of the matrix are zero.  Other arguments as vi_encode_rows. */
+ * of the matrix are zero.  Other arguments as vi_encode_rows.  If the scratch has d_out*d_in/4 + 64
+ * bytes beyond one row's (K+N)*8, its tail is used for pre-multiplied sub-block scales (faster gather). */
 int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, int64_t d_out, int64_t d_in,
                           int transpose, int64_t first_row, int64_t m,
                           int64_t ell, int64_t k, int64_t n,

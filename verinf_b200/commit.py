@@ -43,9 +43,9 @@ class RowCommitter:
     def root(self):
         return self.upper[LIB.vi_merkle_upper_nodes(self.n) - 1] if self.n > 1 else self.leaves[0]
 
-    def _encode(self, msg, r0, cnt, row_offset):
-        check(LIB.vi_encode_rows(msg[r0:r0 + cnt].data_ptr(), cnt, self.ell, self.k, self.n,
-                                 1 if self.seed is not None else 0,
+    def _encode(self, src_rows, r0, cnt, row_offset):
+        """encode `cnt` message rows starting at device pointer `src_rows` into codeword rows r0.."""
+        check(LIB.vi_encode_rows(src_rows, cnt, self.ell, self.k, self.n, 1 if self.seed is not None else 0,
                                  ptr(self.seed), row_offset + r0, None, self.codes[r0:r0 + cnt].data_ptr(),
                                  ptr(self._enc_scratch), self._enc_bytes, stream_ptr()))
 
@@ -58,7 +58,7 @@ class RowCommitter:
         assert msg.is_cuda and msg.dtype == torch.uint64 and msg.is_contiguous()
         assert tuple(msg.shape) == (self.rows, self.ell)
         with torch.cuda.device(self.device):
-            self._encode(msg, 0, self.rows, row_offset)
+            self._encode(msg.data_ptr(), 0, self.rows, row_offset)
             self._hash_and_tree()
         return self.root
 
@@ -82,10 +82,7 @@ class RowCommitter:
                     events.append((r0, cnt, ev))
             for r0, cnt, ev in events:
                 main.wait_event(ev)
-                check(LIB.vi_encode_rows(self._stage[r0:r0 + cnt].data_ptr(), cnt, self.ell, self.k, self.n,
-                                         1 if self.seed is not None else 0, ptr(self.seed), row_offset + r0,
-                                         None, self.codes[r0:r0 + cnt].data_ptr(),
-                                         ptr(self._enc_scratch), self._enc_bytes, stream_ptr()))
+                self._encode(self._stage[r0:r0 + cnt].data_ptr(), r0, cnt, row_offset)
             self._hash_and_tree()
             self._root_host.copy_(self.root, non_blocking=True)
             main.synchronize()

@@ -64,4 +64,49 @@ __device__ __forceinline__ uint64_t lift_any(int qtype, const uint8_t* __restric
     return qtype == Q4_K ? lift<Q4_K>(p, e, S) : qtype == Q5_K ? lift<Q5_K>(p, e, S) : lift<Q6_K>(p, e, S);
 }
 
+// ---- pre-multiplied sub-block scales ---------------------------------------------------------
+// 64 bytes per super-block: Q4_K/Q5_K: 8 x (d*sc, dmin*mn) as float2; Q6_K: 16 x (d*sc) as float.
+// The products are the same separately-rounded fp32 multiplies lift<>() performs, so decoding
+// through the table is bit-identical; it replaces five scattered header byte loads per element
+// by one 8-byte (4-byte) load, which matters when consecutive elements come from different
+// super-blocks (the transposed gather of the fused lift + encode).
+constexpr int TABLE_BYTES_PER_BLOCK = 64;
+
+template <int QT>
+__device__ __forceinline__ void fill_table(const uint8_t* __restrict__ p, int sub, float* __restrict__ t) {
+    if constexpr (QT == Q6_K) {
+        t[sub] = __fmul_rn(ld_half(p + 208), (float)(int)(signed char)__ldg(p + 192 + sub));   // sub in [0,16)
+    } else {
+        uint32_t sc, mn;
+        scale_min(p + 4, sub, sc, mn);                                                          // sub in [0,8)
+        t[2 * sub] = __fmul_rn(ld_half(p), (float)sc);
+        t[2 * sub + 1] = __fmul_rn(ld_half(p + 2), (float)mn);
+    }
+}
+
+template <int QT>
+__device__ __forceinline__ uint64_t lift_tab(const uint8_t* __restrict__ p, const float* __restrict__ t, int e, double S) {
+    if constexpr (QT == Q6_K) {
+        int lo = (__ldg(p + (e >> 7) * 64 + (e & 63)) >> (4 * ((e >> 6) & 1))) & 0xF;
+        int hi = (__ldg(p + 128 + (e >> 7) * 32 + (e & 31)) >> (2 * ((e >> 5) & 3))) & 3;
+        return to_field(__fmul_rn(__ldg(t + (e >> 4)), (float)((lo | (hi << 4)) - 32)), S);
+    } else {
+        const float2 sm = __ldg(reinterpret_cast<const float2*>(t) + (e >> 5));
+        const uint8_t* qs = p + (QT == Q4_K ? 16 : 48);
+        int q = (__ldg(qs + (e >> 6) * 32 + (e & 31)) >> (4 * ((e >> 5) & 1))) & 0xF;
+        if constexpr (QT == Q5_K) q |= ((__ldg(p + 16 + (e & 31)) >> (e >> 5)) & 1) << 4;
+        return to_field(__fsub_rn(__fmul_rn(sm.x, (float)q), sm.y), S);
+    }
+}
+
+__device__ __forceinline__ uint64_t lift_any_tab(int qtype, const uint8_t* __restrict__ raw,
+                                                 const float* __restrict__ table, int64_t widx, double S) {
+    const int64_t b = widx >> 8;
+    const uint8_t* p = raw + b * block_bytes(qtype);
+    const float* t = table + b * (TABLE_BYTES_PER_BLOCK / 4);
+    const int e = (int)(widx & 255);
+    return qtype == Q4_K ? lift_tab<Q4_K>(p, t, e, S) : qtype == Q5_K ? lift_tab<Q5_K>(p, t, e, S)
+                                                                       : lift_tab<Q6_K>(p, t, e, S);
+}
+
 }  // namespace vkq

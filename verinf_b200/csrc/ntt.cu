@@ -152,6 +152,7 @@ struct PassArgs {
     int kq_transpose;
     double kq_S;
     int64_t kq_dout, kq_din, kq_first_row;
+    const float* kq_table;   // pre-multiplied sub-block scales (vkq::fill_table) or null
 };
 
 // Minimum resident CTAs per SM asked of the compiler for the 256-thread tiles (register budget =
@@ -208,7 +209,8 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
                             int64_t f = (a.kq_first_row + item) * a.ell + slot;
                             if (f < a.kq_dout * a.kq_din) {
                                 int64_t widx = a.kq_transpose ? (f % a.kq_dout) * a.kq_din + f / a.kq_dout : f;
-                                x = vkq::lift_any(a.kq_type, a.kq_raw, widx, a.kq_S);
+                                x = a.kq_table ? vkq::lift_any_tab(a.kq_type, a.kq_raw, a.kq_table, widx, a.kq_S)
+                                               : vkq::lift_any(a.kq_type, a.kq_raw, widx, a.kq_S);
                             }
                         }
                     } else if (a.pad_mode == 1) x = vb3::pad_prg(seed, (uint64_t)(a.row_off + item), (uint64_t)(slot - a.ell));
@@ -254,6 +256,21 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
             if (cl < ncols_tile) dst[(uint32_t)cl * a.out_col + (uint32_t)k * a.out_k] = sm[k * CP + cl];
         }
     }
+}
+
+// one thread per (super-block, sub-block): pre-multiplied scales for the fused K-quant loader
+__global__ void __launch_bounds__(256) k_kq_table(const uint8_t* __restrict__ raw, int qtype, int64_t n_blocks,
+                                                  float* __restrict__ table) {
+    const int per = qtype == vkq::Q6_K ? 16 : 8;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_blocks * per) return;
+    const int64_t b = i / per;
+    const int sub = (int)(i - b * per);
+    const uint8_t* p = raw + b * vkq::block_bytes(qtype);
+    float* t = table + b * (vkq::TABLE_BYTES_PER_BLOCK / 4);
+    if (qtype == vkq::Q4_K) vkq::fill_table<vkq::Q4_K>(p, sub, t);
+    else if (qtype == vkq::Q5_K) vkq::fill_table<vkq::Q5_K>(p, sub, t);
+    else vkq::fill_table<vkq::Q6_K>(p, sub, t);
 }
 
 // ---------------------------------------------------------------------------
@@ -582,7 +599,7 @@ extern "C" int64_t vi_encode_scratch_bytes(int64_t m, int64_t k, int64_t n) {
 }
 
 namespace {
-struct KqSrc { const uint8_t* raw; int qtype; int transpose; double S; int64_t d_out, d_in, first_row; };
+struct KqSrc { const uint8_t* raw; int qtype; int transpose; double S; int64_t d_out, d_in, first_row; const float* table; };
 }
 
 static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t ell, int64_t k, int64_t n,
@@ -629,6 +646,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         if (kq) {
             a.kq_raw = kq->raw; a.kq_type = kq->qtype; a.kq_transpose = kq->transpose; a.kq_S = kq->S;
             a.kq_dout = kq->d_out; a.kq_din = kq->d_in; a.kq_first_row = kq->first_row + r0;
+            a.kq_table = kq->table;
         } a.pad_mode = (ell < k) ? pad_mode : 0; a.row_off = row_off + r0;
         a.seed = seed_dev32;
         rc = launch_pass(log1, true, 0, a, cnt, st, vi::PROF_ENC_PASS1);
@@ -675,7 +693,22 @@ extern "C" int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, in
     VI_REQUIRE(qtype == 4 || qtype == 5 || qtype == 6, "kquant encode: qtype must be 4, 5 or 6");
     VI_REQUIRE(d_out > 0 && d_in > 0 && (d_out * d_in) % 256 == 0, "kquant encode: d_out*d_in must be a multiple of 256");
     VI_REQUIRE(first_row >= 0 && raw != nullptr, "kquant encode: bad source");
-    KqSrc kq{raw, qtype, transpose != 0, S, d_out, d_in, first_row};
+    KqSrc kq{raw, qtype, transpose != 0, S, d_out, d_in, first_row, nullptr};
+    // When the scratch has room beyond one row chunk, its tail holds the pre-multiplied sub-block
+    // scales of the whole matrix (64 bytes per super-block), rebuilt on every call.
+    const int64_t n_blocks = d_out * d_in / 256;
+    const int64_t table_bytes = n_blocks * vkq::TABLE_BYTES_PER_BLOCK;
+    const int64_t per_row = (k + (codes ? n : 0)) * 8;
+    if (m > 0 && scratch != nullptr && scratch_bytes >= per_row + table_bytes + 64) {
+        char* tab = (char*)scratch + ((scratch_bytes - table_bytes) & ~int64_t(63));
+        const int per = qtype == 6 ? 16 : 8;
+        const int64_t threads = n_blocks * per;
+        k_kq_table<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(raw, qtype, n_blocks, (float*)tab);
+        int rc = vi::check_launch("k_kq_table");
+        if (rc) return rc;
+        kq.table = (const float*)tab;
+        scratch_bytes = tab - (char*)scratch;
+    }
     return encode_impl(nullptr, &kq, m, ell, k, n, pad_mode, seed_dev32, row_off, polys, codes,
                        scratch, scratch_bytes, stream);
 }

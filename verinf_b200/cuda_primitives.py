@@ -585,7 +585,8 @@ class _Module:
     """Stands in for the reference's JIT extension object (`_ensure_compiled()`), for code
     that reaches for merkle_one_level or the stream-hash trio directly."""
 
-    _stream_pos: dict = {}
+    _stream_pos: dict = {}       # state data_ptr -> rows hashed so far
+    _stream_digests: dict = {}   # state data_ptr -> digests written by the closing update
 
     @staticmethod
     def merkle_one_level(nodes_u32):
@@ -623,11 +624,12 @@ class _Module:
             check(LIB.vi_hash_stream_update(ptr(states), n_cols, total, done, ptr(chunk), n, ptr(dig), stream_ptr()))
         cls._stream_pos[states.data_ptr()] = done + n
         if is_last_chunk:
-            cls._stream_pos[("digest", states.data_ptr())] = dig
+            cls._stream_digests[states.data_ptr()] = dig
 
     @classmethod
     def hash_columns_stream_finalize(cls, states, n_cols, n_chunks_total):
-        return cls._stream_pos.pop(("digest", states.data_ptr()))
+        cls._stream_pos.pop(states.data_ptr(), None)
+        return cls._stream_digests.pop(states.data_ptr())
 
 
 def _ensure_compiled():
