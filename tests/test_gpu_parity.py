@@ -548,3 +548,23 @@ def test_commit_rows_sharded_single_process(cp):
     root, levels, codes = D.commit_rows_sharded(msg, 600, D.CudaBackend(128, 512))
     want_root, _, want_codes = cp.commit_rows(msg, 128, 512)
     assert torch.equal(root, want_root) and torch.equal(codes.view(torch.int64), want_codes.view(torch.int64))
+
+
+def test_more_rows_than_a_grid_dimension(cp):
+    """70000 rows in one call: the reference's batched kernels stop at 65535 rows (one block-row per
+    message, layergkr/gpu.py:33-35); here rows are tiled, so there is no such cap."""
+    rng = np.random.default_rng(65536)
+    m = 70000
+    a = rnd_field(rng, (m, 64))
+    x = dev(a)
+    cp.ntt_forward_batched(x)
+    got = host(x)
+    idx = [0, 1, 65534, 65535, 65536, m - 1]
+    assert np.array_equal(got[idx], oracle.ntt_batched(a[idx]))
+    msg = rnd_field(rng, (m, 6))
+    _, codes = cp.encode_rows(dev(msg), 8, 32, need_polys=False)
+    padded = np.zeros((len(idx), 8), dtype=np.uint64)
+    padded[:, :6] = msg[idx]
+    assert np.array_equal(host(codes)[idx], oracle.encode_rows(padded, 32, want_polys=False)[1])
+    leaves = cp.hash_columns_streamed(codes)
+    assert np.array_equal(leaves.cpu().numpy(), oracle.hash_columns(host(codes)))
