@@ -34,6 +34,7 @@ def test_size_helpers(lib):
     assert L.vi_merkle_upper_nodes(4096) == 4095
     assert L.vi_ntt_scratch_bytes(10, 1024) == 0
     assert L.vi_ntt_scratch_bytes(1, 1 << 16) == (1 << 16) * 8
+    assert L.vi_ntt_scratch_bytes(1, 1 << 24) == (1 << 24) * 8
     assert L.vi_ntt_scratch_bytes(10 ** 6, 1 << 16) % ((1 << 16) * 8) == 0
     assert L.vi_encode_scratch_bytes(1, 1 << 10, 1 << 12) == ((1 << 10) + (1 << 12)) * 8
     assert L.vi_encode_scratch_bytes(0, 8, 32) == 0
@@ -59,7 +60,7 @@ def test_argument_validation_without_gpu(lib):
     assert L.vi_ntt_batched(p, 1, 12, 0, None, 0, None) != 0 and "power of 2" in _err(lib)
     assert L.vi_ntt_batched(p, 1, 1, 0, None, 0, None) != 0
     assert L.vi_ntt_batched(p, -1, 16, 0, None, 0, None) != 0
-    assert L.vi_ntt_batched(p, 1, 1 << 21, 0, None, 0, None) != 0 and "exceeds" in _err(lib)
+    assert L.vi_ntt_batched(p, 1, 1 << 25, 0, None, 0, None) != 0 and "exceeds" in _err(lib)
     assert L.vi_ntt_batched(p, 0, 16, 0, None, 0, None) == 0                  # empty batch is fine
     assert L.vi_encode_rows(p, 1, 9, 8, 32, 0, None, 0, p, p, p, 1 << 20, None) != 0 and "ELL" in _err(lib)
     assert L.vi_encode_rows(p, 1, 8, 12, 48, 0, None, 0, p, p, p, 1 << 20, None) != 0

@@ -108,12 +108,13 @@ def test_ntt_batched_vs_oracle(cp, logn, m):
 
 def test_ntt_large_roundtrip_and_errors(cp):
     rng = np.random.default_rng(7)
-    a = rnd_field(rng, (2, 1 << 20))
-    x = dev(a)
-    cp.ntt_forward_batched(x)
-    assert np.array_equal(host(x)[1], oracle.ntt(a[1]))
-    cp.ntt_inverse_batched(x)
-    assert np.array_equal(host(x), a)
+    for logn, m in ((20, 2), (21, 1), (22, 2), (24, 1)):
+        a = rnd_field(rng, (m, 1 << logn))
+        x = dev(a)
+        cp.ntt_forward_batched(x)
+        assert np.array_equal(host(x)[m - 1], oracle.ntt(a[m - 1])), logn
+        cp.ntt_inverse_batched(x)
+        assert np.array_equal(host(x), a), logn
     with pytest.raises(RuntimeError):
         cp.ntt_forward(dev(np.arange(12)))
     with pytest.raises(RuntimeError):
@@ -213,6 +214,23 @@ def test_encode_vs_oracle(cp, ell, k, n, m, pad):
             ext[:, :k] = cp.gl_mul_rowvec(full, g)
             cp.ntt_forward_batched(ext)
             assert torch.equal(ext.view(torch.int64), codes.view(torch.int64))
+
+
+@pytest.mark.parametrize("ell,k,n,m", [((1 << 21) - 5, 1 << 21, 1 << 22, 2), (1 << 23, 1 << 23, 1 << 24, 1)])
+def test_encode_long_rows(cp, ell, k, n, m):
+    """K above 2^20: tile DFT lengths 2048 and 4096 (4 and 2 columns per tile)"""
+    rng = np.random.default_rng(k % 1009)
+    msg = rnd_field(rng, (m, ell))
+    seed = bytes(rng.integers(0, 256, size=32, dtype=np.uint8))
+    padded = np.zeros((m, k), dtype=np.uint64)
+    padded[:, :ell] = msg
+    if ell < k:
+        padded[:, ell:] = oracle.row_prg(seed, 5, m, k - ell)
+    want_p, want_c = oracle.encode_rows(padded, n)
+    seed_t = torch.tensor(list(seed), dtype=torch.uint8, device="cuda")
+    polys, codes = cp.encode_rows(dev(msg), k, n, master_seed=seed_t, row_offset=5)
+    assert np.array_equal(host(polys), want_p)
+    assert np.array_equal(host(codes), want_c)
 
 
 def test_encode_edge_cases(cp):

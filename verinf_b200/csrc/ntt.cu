@@ -433,7 +433,8 @@ int get_twist(int64_t K, int64_t N, const uint64_t** out) {
     return VI_OK;
 }
 
-constexpr int MAX_LOGL = 10;
+constexpr int MAX_LOGL = 12;      // tile DFT length up to 4096 (2 columns per tile) -> two-pass transforms up to 2^24
+constexpr int SINGLE_LOGL = 10;   // transforms up to this length run as one pass over 16-row tiles
 
 // columns per tile for a DFT length 2^logL given ncols available
 int pick_logC(int logL, int64_t ncols) {
@@ -442,8 +443,8 @@ int pick_logC(int logL, int64_t ncols) {
     if (logC > 9 - logTPC) logC = 9 - logTPC;          // at most 512 threads
     int need = vi::ilog2(ncols);
     if (need < 4) need = 4;
-    if (logC > need) logC = need;
-    if (logC < 3) logC = 3;
+    if (logC > need && logC > 4) logC = need;
+    if (logC < 1) logC = 1;
     return logC;
 }
 int tile_threads(int logL, int logC) {
@@ -470,7 +471,7 @@ int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st, i
     switch (logL) {
 #define VI_CASE(x) case x: return launch_pass_t<x, INV, MODE>(a, items, st, tag);
         VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
-        VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
+        VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10) VI_CASE(11) VI_CASE(12)
 #undef VI_CASE
     }
     return vi::fail(VI_ERR_LIMIT, "unsupported tile length 2^%d", logL);
@@ -500,7 +501,7 @@ int launch_mid(int logL, const MidArgs& a, int64_t items, cudaStream_t st) {
     switch (logL) {
 #define VI_CASE(x) case x: return launch_mid_t<x>(a, items, st);
         VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
-        VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
+        VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10) VI_CASE(11) VI_CASE(12)
 #undef VI_CASE
     }
     return vi::fail(VI_ERR_LIMIT, "unsupported tile length 2^%d", logL);
@@ -528,7 +529,7 @@ int64_t chunk_bytes() {
 }  // namespace
 
 extern "C" int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n) {
-    if (n <= (int64_t(1) << MAX_LOGL) || m <= 0) return 0;
+    if (n <= (int64_t(1) << SINGLE_LOGL) || m <= 0) return 0;
     int64_t row = n * 8;
     int64_t rows = chunk_bytes() / row;
     if (rows < 1) rows = 1;
@@ -547,7 +548,7 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
     VI_REQUIRE(rows != nullptr, "ntt: null data pointer");
     const bool inv = inverse != 0;
     const uint64_t scale = inv ? inv_pow2(logn) : 1;
-    if (logn <= MAX_LOGL) {
+    if (logn <= SINGLE_LOGL) {
         PassArgs a{};
         a.in = rows; a.out = rows;
         a.logC = pick_logC(logn, m);
