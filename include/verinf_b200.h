@@ -139,6 +139,23 @@ int64_t vi_merkle_upper_nodes(int64_t n_leaves);
 int vi_merkle_build(const uint8_t* leaves, int64_t n_leaves, uint8_t* upper, void* stream);
 int vi_merkle_level(const uint8_t* nodes, int64_t n_nodes, uint8_t* parents, void* stream);
 
+/* ---- Column openings ----------------------------------------------------------------
+ * vi_open_columns replaces `codes.index_select(1, Q_set)` + per-column clone/cat
+ * (prover/core.py:1304-1320): out[t*out_stride + row0 + r] = mat[r*n + cols[t]] for r < m,
+ * t < T, so a matrix that arrives in row chunks fills one (T, total_rows) buffer, each
+ * opened column contiguous.  cols is a device array; an index outside [0, n) yields zeros.
+ * vi_merkle_paths replaces merkle_path over a host copy of the tree (prover/core.py:294-317):
+ * for each queried leaf idx[t] and level l < depth (= vi_merkle_depth(n_leaves)),
+ * siblings[(t*depth + l)*32 ..] is the sibling node (the node itself where an odd level has
+ * no sibling) and sides[t*depth + l] is 1 when the path node is a left child, else 0.
+ * leaves/upper are the buffers of vi_merkle_build (16-byte aligned); idx is a device
+ * array, an index outside [0, n_leaves) yields the path of leaf 0. */
+int vi_open_columns(const uint64_t* mat, int64_t m, int64_t n, const int64_t* cols_dev, int64_t T,
+                    uint64_t* out, int64_t out_stride, int64_t row0, void* stream);
+int vi_merkle_depth(int64_t n_leaves);
+int vi_merkle_paths(const uint8_t* leaves, int64_t n_leaves, const uint8_t* upper,
+                    const int64_t* idx_dev, int64_t T, uint8_t* siblings, uint8_t* sides, void* stream);
+
 /* ---- K-quant lift -----------------------------------------------------------------
  * replaces kquant_to_field (prover/kquant_cuda.py:60-177): raw GGUF super-blocks ->
  * field integers round_half_even(double(v) * S), negative values as p - |v|, in stored

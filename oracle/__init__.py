@@ -35,6 +35,7 @@ def lib():
             getattr(L, name).argtypes = [u64, u64]
         L.or_gl_inv.restype = u64; L.or_gl_inv.argtypes = [u64]
         L.or_root_of_unity.restype = u64; L.or_root_of_unity.argtypes = [u64]
+        L.or_gl_matmul.argtypes = [p, p, p, i64, i64, i64]; L.or_gl_matmul.restype = None
         L.or_ntt.argtypes = [p, i64, C.c_int]; L.or_ntt.restype = None
         L.or_ntt_batched.argtypes = [p, i64, i64, C.c_int]; L.or_ntt_batched.restype = None
         L.or_encode_rows.argtypes = [p, i64, i64, i64, p, p]; L.or_encode_rows.restype = None
@@ -76,6 +77,16 @@ def gl_mul(a, b): return lib().or_gl_mul(int(a), int(b))
 def gl_pow(a, e): return lib().or_gl_pow(int(a), int(e))
 def gl_inv(a): return lib().or_gl_inv(int(a))
 def root_of_unity(n): return lib().or_root_of_unity(int(n))
+
+
+def gl_matmul(A, B):
+    A, B = _u64(A), _u64(B)
+    m, k = A.shape
+    k2, n = B.shape
+    assert k == k2
+    out = np.empty((m, n), dtype=np.uint64)
+    lib().or_gl_matmul(_ptr(A), _ptr(B), _ptr(out), m, k, n)
+    return out
 
 
 # ---- NTT / encode ------------------------------------------------------
@@ -136,6 +147,28 @@ def merkle_levels(leaves):
             break
         n = (n + 1) // 2
     return out
+
+
+def merkle_path(levels, idx: int):
+    """Opening path of leaf `idx`: per level below the root (sibling bytes, side), the sibling
+    being the node itself where an odd level has none, side = 1 when the path node is the left
+    child.  Follows merkle_path (prover/core.py:305-317) on the levels of merkle_levels()."""
+    path = []
+    for level in levels[:-1]:
+        sib = idx ^ 1
+        if sib >= len(level):
+            sib = idx
+        path.append((bytes(level[sib].tobytes()), 1 if (idx & 1) == 0 else 0))
+        idx //= 2
+    return path
+
+
+def merkle_verify(leaf: bytes, path, root: bytes) -> bool:
+    """Recompute the root from a leaf and its path (merkle_verify, prover/core.py:318-323)."""
+    cur = leaf
+    for sib, side in path:
+        cur = blake3(cur + sib) if side == 1 else blake3(sib + cur)
+    return cur == root
 
 
 def row_prg(seed: bytes, row_offset: int, n_rows: int, slack: int):

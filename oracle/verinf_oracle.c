@@ -46,6 +46,18 @@ uint64_t or_gl_pow(uint64_t a, uint64_t e) { return f_pow(a, e); }
 uint64_t or_gl_inv(uint64_t a) { return f_inv(a); }
 
 /* primitive n-th root of unity: goldilocks_ref.py:45-49 (7^((p-1)/n)) */
+/* C = A.B mod p, row-major (m,k).(k,n); definition of gl_matmul
+ * (prover/cuda_primitives.py:1086-1106, prover/kernels/gl_matmul.cuh) */
+void or_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < m; ++i)
+        for (int64_t j = 0; j < n; ++j) {
+            uint64_t acc = 0;
+            for (int64_t l = 0; l < k; ++l) acc = f_add(acc, f_mul(A[i * k + l], B[l * n + j]));
+            C[i * n + j] = acc;
+        }
+}
+
 uint64_t or_root_of_unity(uint64_t n) { return f_pow(7, (GL_P - 1) / n); }
 
 /* ------------------------------------------------------------------ */

@@ -213,7 +213,36 @@ def sumcheck_vectors():
     np.savez_compressed(HERE / "sumcheck_vectors.npz", **out)
 
 
+def merkle_path_vectors():
+    """Opening paths from rs.build_tree + rs.merkle_path (same convention as
+    prover/core.merkle_path) for every leaf of trees with 1, 2, 5, 8 and 13 leaves; each path is
+    checked with protocol.merkle_verify before it is stored."""
+    rng = random.Random(2024)
+    out = {}
+    for n in (1, 2, 5, 8, 13):
+        leaves = [bytes(rng.randrange(256) for _ in range(32)) for _ in range(n)]
+        levels = rs.build_tree(leaves)
+        depth = len(levels) - 1
+        sib = np.zeros((n, depth, 32), dtype=np.uint8)
+        side = np.zeros((n, depth), dtype=np.uint8)
+        for i in range(n):
+            path = rs.merkle_path(levels, i)
+            assert protocol.merkle_verify(leaves[i], path, levels[-1][0])
+            for l, (s, d) in enumerate(path):
+                sib[i, l] = np.frombuffer(s, dtype=np.uint8)
+                side[i, l] = d
+        out[f"n{n}_leaves"] = np.frombuffer(b"".join(leaves), dtype=np.uint8).reshape(n, 32)
+        out[f"n{n}_root"] = np.frombuffer(levels[-1][0], dtype=np.uint8)
+        out[f"n{n}_siblings"] = sib
+        out[f"n{n}_sides"] = side
+    np.savez_compressed(HERE / "merkle_path_vectors.npz", **out)
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 2 and sys.argv[2] == "merkle_paths":      # only this fixture
+        merkle_path_vectors()
+        sys.exit(0)
+    merkle_path_vectors()
     field_vectors()
     ntt_vectors()
     hash_vectors()

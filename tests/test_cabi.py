@@ -76,6 +76,12 @@ def test_argument_validation_without_gpu(lib):
     assert L.vi_hash_stream_update(p, 8, 256, 128, p, 256, p, None) != 0
     assert L.vi_hash_columns(p, 4096, 200000, p, None, 0, None) != 0 and "scratch" in _err(lib)
     assert L.vi_challenge(p, p, 9, None, 4, p, None) != 0 and "label" in _err(lib)
+    assert L.vi_open_columns(p, 4, 8, p, 2, p, 3, 0, None) != 0 and "stride" in _err(lib)
+    assert L.vi_open_columns(p, -1, 8, p, 2, p, 3, 0, None) != 0
+    assert L.vi_open_columns(p, 0, 8, p, 2, p, 3, 0, None) == 0
+    assert L.vi_merkle_paths(p, 0, p, p, 1, p, p, None) != 0
+    assert L.vi_merkle_paths(p, 1, p, p, 5, p, p, None) == 0                  # a single leaf has an empty path
+    assert [L.vi_merkle_depth(n) for n in (1, 2, 3, 5, 8, 9, 4096)] == [0, 1, 2, 3, 3, 4, 12]
     coefs = (C.c_uint64 * 1)(1)
     nfac = (C.c_int32 * 1)(5)
     fac = (C.c_int32 * 4)(0, 1, 2, 3)

@@ -468,6 +468,19 @@ def test_linear_algebra(cp):
     C = host(cp.gl_matmul(dev(A), dev(B)))
     for (i, j) in ((0, 0), (36, 40), (17, 3)):
         assert int(C[i, j]) == sum(int(A[i, l]) * int(B[l, j]) for l in range(65)) % P
+    # tile edges, the unaligned loader (odd n / odd k), more than one reduction period (k > 1024)
+    for (m_, k_, n_) in ((64, 32, 32), (70, 2100, 45), (130, 1025, 64), (3, 1, 2), (64, 4096, 96), (33, 999, 34)):
+        A2, B2 = rnd_field(rng, (m_, k_)), rnd_field(rng, (k_, n_))
+        assert np.array_equal(host(cp.gl_matmul(dev(A2), dev(B2))), oracle.gl_matmul(A2, B2)), (m_, k_, n_)
+    # largest operands: every limb product and every accumulator at its bound
+    A3 = np.full((64, 3072), P - 1, dtype=np.uint64)
+    B3 = np.full((3072, 32), P - 1, dtype=np.uint64)
+    assert np.array_equal(host(cp.gl_matmul(dev(A3), dev(B3))), oracle.gl_matmul(A3, B3))
+    A3[:] = np.uint64(0xFFFFFFFEFFFFFFFF)      # below p, both 32-bit limbs of a near their maximum
+    B3[:] = np.uint64(0xFFFFEFFFFFFFFFFF)      # below p, the two 22-bit limbs of b all ones
+    assert np.array_equal(host(cp.gl_matmul(dev(A3), dev(B3))), oracle.gl_matmul(A3, B3))
+    z = cp.gl_matmul(dev(A2[:, :0]), dev(B2[:0]))
+    assert tuple(z.shape) == (33, 34) and not host(z).any()
     v = rnd_field(rng, 65)
     w = host(cp.gl_matvec(dev(A), dev(v)))
     assert [int(x) for x in w] == [sum(int(a) * int(b) for a, b in zip(A[i], v)) % P for i in range(37)]
@@ -586,3 +599,82 @@ def test_more_rows_than_a_grid_dimension(cp):
     assert np.array_equal(host(codes)[idx], oracle.encode_rows(padded, 32, want_polys=False)[1])
     leaves = cp.hash_columns_streamed(codes)
     assert np.array_equal(leaves.cpu().numpy(), oracle.hash_columns(host(codes)))
+
+
+# ---------------------------------------------------------------- openings ----
+@pytest.mark.parametrize("n", [1, 2, 5, 8, 13])
+def test_merkle_paths_golden(cp, golden, n):
+    from verinf_b200 import commit
+    g = golden.merkle_path_vectors
+    leaves = torch.from_numpy(g[f"n{n}_leaves"].copy()).cuda()
+    root, levels = cp.merkle_build_blake3(leaves)
+    assert root.cpu().numpy().tobytes() == g[f"n{n}_root"].tobytes()
+    upper = torch.empty((1, 32), dtype=torch.uint8, device="cuda") if n == 1 else torch.cat(levels[1:]).contiguous()
+    sib, sides = commit.merkle_paths(leaves, upper, list(range(n)))
+    assert np.array_equal(sib.cpu().numpy(), g[f"n{n}_siblings"])
+    assert np.array_equal(sides.cpu().numpy(), g[f"n{n}_sides"])
+
+
+@pytest.mark.parametrize("n", [1000, 4097, 65536])
+def test_merkle_paths_vs_oracle(cp, n):
+    from verinf_b200 import commit
+    rng = np.random.default_rng(n)
+    leaves_h = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    leaves = torch.from_numpy(leaves_h).cuda()
+    root, levels = cp.merkle_build_blake3(leaves)
+    upper = torch.cat(levels[1:]).contiguous()
+    q = sorted(set([0, 1, n - 1, n - 2, n // 2] + [int(v) for v in rng.integers(0, n, size=40)]))
+    sib, sides = commit.merkle_paths(leaves, upper, q)
+    want_levels = oracle.merkle_levels(leaves_h)
+    got = commit.paths_as_reference(sib, sides)
+    root_b = root.cpu().numpy().tobytes()
+    for t, j in enumerate(q):
+        assert got[t] == oracle.merkle_path(want_levels, j)
+        assert oracle.merkle_verify(leaves_h[j].tobytes(), got[t], root_b)
+    with pytest.raises(RuntimeError):
+        commit.merkle_paths(leaves, upper, [n])
+
+
+def test_open_columns_and_committer_open(cp):
+    from verinf_b200 import commit
+    rng = np.random.default_rng(8)
+    rows, ell, k, n = 300, 48, 64, 256
+    msg = rnd_field(rng, (rows, ell))
+    seed_t = torch.arange(32, dtype=torch.uint8, device="cuda")
+    com = commit.RowCommitter(rows, ell, k, n, master_seed=seed_t)
+    root = com.commit(dev(msg), row_offset=3).cpu().numpy().tobytes()
+    q = [0, 255, 17, 17, 128, 3]
+    cols, sib, sides = com.open(q)
+    codes = host(com.codes)
+    assert np.array_equal(host(cols), codes[:, q].T)
+    leaves = oracle.hash_columns(codes)
+    for t, j in enumerate(q):
+        path = commit.paths_as_reference(sib, sides)[t]
+        assert oracle.merkle_verify(leaves[j].tobytes(), path, root)
+        # the opened column hashes to the leaf the path authenticates (core.py:1086 check)
+        assert oracle.blake3(host(cols)[t].tobytes()) == leaves[j].tobytes()
+    with pytest.raises(RuntimeError):
+        com.open([256])
+    assert tuple(commit.open_columns(com.codes, []).shape) == (0, rows)
+
+
+@pytest.mark.parametrize("chunks", [[600], [100, 1, 127, 300, 72], [128, 128, 128, 216], [1] * 3 + [597]])
+def test_stream_committer_equals_one_shot(cp, chunks):
+    from verinf_b200 import commit
+    rng = np.random.default_rng(5)
+    total, ell, k, n = sum(chunks), 100, 128, 512
+    msg = dev(rnd_field(rng, (total, ell)))
+    seed_t = torch.arange(32, dtype=torch.uint8, device="cuda")
+    want_root, want_levels, want_codes = cp.commit_rows(msg, k, n, master_seed=seed_t, row_offset=77)
+    q = [5, 500, 0, 511]
+    sc = commit.StreamCommitter(total, ell, k, n, master_seed=seed_t, row_offset=77, open_cols=q, max_chunk_rows=256)
+    r0 = 0
+    for c in chunks:
+        sc.update(msg[r0:r0 + c])
+        r0 += c
+    root = sc.finalize()
+    assert torch.equal(root, want_root)
+    assert torch.equal(sc.opened.view(torch.int64), want_codes.view(torch.int64)[:, q].T)
+    sib, sides = sc.paths()
+    levels = oracle.merkle_levels(want_levels[0].cpu().numpy())
+    assert commit.paths_as_reference(sib, sides) == [oracle.merkle_path(levels, j) for j in q]

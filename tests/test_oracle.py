@@ -107,3 +107,30 @@ def test_sumcheck_vectors(golden, name):
     assert claim == int(g[f"{name}_claim"][0])
     want = g[f"{name}_polys"]
     assert np.array_equal(samples[:, :want.shape[1]], want)
+
+
+@pytest.mark.parametrize("n", [1, 2, 5, 8, 13])
+def test_merkle_path_vectors(golden, n):
+    g = golden.merkle_path_vectors
+    leaves = g[f"n{n}_leaves"]
+    levels = oracle.merkle_levels(leaves)
+    root = g[f"n{n}_root"].tobytes()
+    assert levels[-1][0].tobytes() == root
+    for i in range(n):
+        path = oracle.merkle_path(levels, i)
+        assert [s for s, _ in path] == [g[f"n{n}_siblings"][i, l].tobytes() for l in range(len(path))]
+        assert [d for _, d in path] == [int(v) for v in g[f"n{n}_sides"][i]]
+        assert oracle.merkle_verify(leaves[i].tobytes(), path, root)
+        assert n == 1 or not oracle.merkle_verify(leaves[(i + 1) % n].tobytes(), path, root)
+
+
+def test_matmul_against_python_integers():
+    rng = np.random.default_rng(12)
+    A = rng.integers(0, P, size=(5, 37), dtype=np.uint64)
+    B = rng.integers(0, P, size=(37, 4), dtype=np.uint64)
+    A[0, :] = P - 1
+    B[:, 0] = P - 1
+    got = oracle.gl_matmul(A, B)
+    for i in range(5):
+        for j in range(4):
+            assert int(got[i, j]) == sum(int(A[i, l]) * int(B[l, j]) for l in range(37)) % P

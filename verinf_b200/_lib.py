@@ -40,6 +40,9 @@ SIGNATURES = {
     "vi_merkle_upper_nodes": (_i64, [_i64]),
     "vi_merkle_build": (_int, [_p, _i64, _p, _p]),
     "vi_merkle_level": (_int, [_p, _i64, _p, _p]),
+    "vi_merkle_depth": (_int, [_i64]),
+    "vi_merkle_paths": (_int, [_p, _i64, _p, _p, _i64, _p, _p, _p]),
+    "vi_open_columns": (_int, [_p, _i64, _i64, _p, _i64, _p, _i64, _i64, _p]),
     "vi_kquant_to_field": (_int, [_p, _i64, _int, _dbl, _p, _p]),
     "vi_kquant_encode_rows": (_int, [_p, _int, _dbl, _i64, _i64, _int, _i64, _i64, _i64, _i64, _i64,
                                      _int, _p, _i64, _p, _p, _p, _i64, _p]),

@@ -66,33 +66,151 @@ __global__ void k_poly_eval(const uint64_t* __restrict__ coeffs, int64_t m, int6
     out[r * k + p] = acc;
 }
 
-// C = A.B mod p with 32x32 output tiles staged through shared memory.
-__global__ void __launch_bounds__(256) k_matmul(const uint64_t* __restrict__ A, const uint64_t* __restrict__ B,
-                                                uint64_t* __restrict__ C, int64_t m, int64_t k, int64_t n) {
-    __shared__ uint64_t sa[32][33], sb[32][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8 threads, 4 rows each
-    const int64_t row0 = (int64_t)blockIdx.y * 32, col0 = (int64_t)blockIdx.x * 32;
-    uint64_t acc[4] = {0, 0, 0, 0};
-    for (int64_t l0 = 0; l0 < k; l0 += 32) {
+// C = A.B mod p with lazily reduced accumulation.
+// CTA tile 64 x 32 outputs, k in slices of 32, 256 threads, 4 x 2 outputs per thread.  Each
+// 64 x 64 -> 128-bit product is never formed: a is split into two 32-bit limbs, b into limbs of
+// 22 + 22 + 20 bits, and the six limb products (< 2^54) are summed in six 64-bit accumulators by
+// one wide multiply-add each (FMA pipe, no carry chain).  1024 products fit before an
+// accumulator could overflow, so every 32 slices (and at the end) the six sums are recombined
+// sum_ij acc_ij * 2^(32 i + 22 j), reduced mod p and added into C.  Tiles arrive through
+// cp.async into a double buffer when they are whole and 16-byte aligned, else through guarded
+// loads with zero fill.
+#ifndef VI_MM_MINB
+#define VI_MM_MINB 2      // resident CTAs per SM asked of the compiler (128 registers per thread)
+#endif
+constexpr int MM_TM = 64, MM_TN = 32, MM_TK = 32, MM_AS = 34;   // MM_AS: row stride of the A tile (u64)
+constexpr int MM_SMEM = 2 * (MM_TM * MM_AS + MM_TK * MM_TN) * 8;
+constexpr int MM_FLUSH = 32;                                      // slices between reductions
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// acc * 2^S mod p for any 64-bit acc, S < 128
+template <int S>
+__device__ __forceinline__ uint64_t shifted_mod(uint64_t acc) {
+    if constexpr (S == 0) return vgl::reduce128(acc, 0);
+    else if constexpr (S < 64) return vgl::reduce128(acc << S, acc >> (64 - S));
+    else return vgl::reduce128(0, shifted_mod<S - 64>(acc));
+}
+
+__global__ void __launch_bounds__(256, VI_MM_MINB) k_matmul(const uint64_t* __restrict__ A, const uint64_t* __restrict__ B,
+                                                   uint64_t* __restrict__ C, int64_t m, int64_t k, int64_t n) {
+    extern __shared__ __align__(16) uint64_t mm_smem[];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int64_t row0 = (int64_t)blockIdx.y * MM_TM, col0 = (int64_t)blockIdx.x * MM_TN;
+    const int64_t nslices = (k + MM_TK - 1) / MM_TK;
+    const bool a_fast = (k % 2 == 0) && (((uintptr_t)A) % 16 == 0) && row0 + MM_TM <= m;
+    const bool b_fast = (n % 2 == 0) && (((uintptr_t)B) % 16 == 0) && col0 + MM_TN <= n;
+
+    auto load_slice = [&](int64_t s, int buf) {
+        uint64_t* sa = mm_smem + buf * (MM_TM * MM_AS + MM_TK * MM_TN);
+        uint64_t* sb = sa + MM_TM * MM_AS;
+        const int64_t l0 = s * MM_TK;
+        const bool whole_k = l0 + MM_TK <= k;
+        if (a_fast && whole_k) {
+            // 64 rows x 16 chunks of 16 bytes: 4 per thread
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            int r = ty + 8 * q;
-            sa[r][tx] = (row0 + r < m && l0 + tx < k) ? A[(row0 + r) * k + l0 + tx] : 0;
-            sb[r][tx] = (l0 + r < k && col0 + tx < n) ? B[(l0 + r) * n + col0 + tx] : 0;
+            for (int q = 0; q < 4; ++q) {
+                int e = tid + 256 * q, r = e >> 4, c = e & 15;
+                cp_async16(sa + r * MM_AS + 2 * c, A + (row0 + r) * k + l0 + 2 * c);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                int e = tid + 256 * q, r = e >> 5, l = e & 31;
+                sa[r * MM_AS + l] = (row0 + r < m && l0 + l < k) ? A[(row0 + r) * k + l0 + l] : 0;
+            }
+        }
+        if (b_fast && whole_k) {
+            // 32 rows x 16 chunks of 16 bytes: 2 per thread
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                int e = tid + 256 * q, l = e >> 4, c = e & 15;
+                cp_async16(sb + l * MM_TN + 2 * c, B + (l0 + l) * n + col0 + 2 * c);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                int e = tid + 256 * q, l = e >> 5, c = e & 31;
+                sb[l * MM_TN + c] = (l0 + l < k && col0 + c < n) ? B[(l0 + l) * n + col0 + c] : 0;
+            }
+        }
+        cp_async_commit();
+    };
+
+    uint64_t acc[4][2][6];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int t = 0; t < 6; ++t) acc[q][c][t] = 0;
+    if (nslices > 0) load_slice(0, 0);
+    for (int64_t s = 0; s < nslices; ++s) {
+        const int buf = (int)(s & 1);
+        if (s + 1 < nslices) { load_slice(s + 1, buf ^ 1); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        const uint64_t* sa = mm_smem + buf * (MM_TM * MM_AS + MM_TK * MM_TN);
+        const uint64_t* sb = sa + MM_TM * MM_AS;
+#pragma unroll 1
+        for (int l = 0; l < MM_TK; ++l) {
+            const uint4 bb = *reinterpret_cast<const uint4*>(sb + l * MM_TN + 2 * tx);
+            const uint64_t bv[2] = {vgl::pack(bb.x, bb.y), vgl::pack(bb.z, bb.w)};
+            uint32_t bl[2][3];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                bl[c][0] = (uint32_t)bv[c] & 0x3FFFFFu;
+                bl[c][1] = (uint32_t)(bv[c] >> 22) & 0x3FFFFFu;
+                bl[c][2] = (uint32_t)(bv[c] >> 44);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint64_t av = sa[(ty * 4 + q) * MM_AS + l];
+                const uint32_t a0 = (uint32_t)av, a1 = (uint32_t)(av >> 32);
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) {
+                        acc[q][c][j] += (uint64_t)a0 * bl[c][j];
+                        acc[q][c][3 + j] += (uint64_t)a1 * bl[c][j];
+                    }
+            }
         }
         __syncthreads();
-#pragma unroll 8
-        for (int l = 0; l < 32; ++l) {
-            uint64_t bv = sb[l][tx];
+        if ((s + 1) % MM_FLUSH == 0 || s + 1 == nslices) {
+            const bool first = s < MM_FLUSH;           // nothing has been written to C yet
 #pragma unroll
-            for (int q = 0; q < 4; ++q) acc[q] = add(acc[q], mul(sa[ty + 8 * q][l], bv));
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint64_t* a6 = acc[q][c];
+                    uint64_t v = shifted_mod<0>(a6[0]);
+                    v = add(v, shifted_mod<22>(a6[1]));
+                    v = add(v, shifted_mod<44>(a6[2]));
+                    v = add(v, shifted_mod<32>(a6[3]));
+                    v = add(v, shifted_mod<54>(a6[4]));
+                    v = add(v, shifted_mod<76>(a6[5]));
+                    const int64_t r = row0 + ty * 4 + q, cc = col0 + 2 * tx + c;
+                    if (r < m && cc < n) C[r * n + cc] = first ? v : add(C[r * n + cc], v);
+#pragma unroll
+                    for (int t = 0; t < 6; ++t) a6[t] = 0;
+                }
         }
-        __syncthreads();
     }
+    if (nslices == 0) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        int64_t r = row0 + ty + 8 * q;
-        if (r < m && col0 + tx < n) C[r * n + col0 + tx] = acc[q];
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int64_t r = row0 + ty * 4 + q, cc = col0 + 2 * tx + c;
+                if (r < m && cc < n) C[r * n + cc] = 0;
+            }
     }
 }
 
@@ -282,9 +400,12 @@ extern "C" int vi_poly_eval(const uint64_t* coeffs, int64_t m, int64_t d, const 
 extern "C" int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n, void* stream) {
     VI_REQUIRE(m >= 0 && k >= 0 && n >= 0, "gl_matmul: negative size");
     if (m == 0 || n == 0) return VI_OK;
-    dim3 grid((unsigned)((n + 31) / 32), (unsigned)((m + 31) / 32));
-    VI_REQUIRE(grid.y <= 65535, "gl_matmul: too many rows for one launch (m <= 2097120)");
-    k_matmul<<<grid, 256, 0, (cudaStream_t)stream>>>(A, B, C, m, k, n);
+    VI_REQUIRE(A && B && C || k == 0, "gl_matmul: null pointer");
+    VI_REQUIRE(C != A && C != B, "gl_matmul: the output must not alias an input");
+    dim3 grid((unsigned)((n + MM_TN - 1) / MM_TN), (unsigned)((m + MM_TM - 1) / MM_TM));
+    VI_REQUIRE(grid.y <= 65535, "gl_matmul: too many rows for one launch (m <= 4194240)");
+    VI_CUDA(cudaFuncSetAttribute(k_matmul, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM));
+    k_matmul<<<grid, 256, MM_SMEM, (cudaStream_t)stream>>>(A, B, C, m, k, n);
     return vi::check_launch("k_matmul");
 }
 
