@@ -139,6 +139,24 @@ int64_t vi_merkle_upper_nodes(int64_t n_leaves);
 int vi_merkle_build(const uint8_t* leaves, int64_t n_leaves, uint8_t* upper, void* stream);
 int vi_merkle_level(const uint8_t* nodes, int64_t n_nodes, uint8_t* parents, void* stream);
 
+/* ---- Evaluation-domain fold of row products -----------------------------------------
+ * The q_lin and p_0 folds multiply rows of coefficient polynomials pairwise and sum the
+ * products over the rows (prover/core.py:1892-1911 `_compute_q_lin_inner_chunk`, fused
+ * branch; prover/core.py:2166-2181 `compute_p_0_streaming`).  The reference builds zero-padded
+ * copies, runs ntt_forward_batched on both, gl_mul, a transposed copy and gl_matvec.
+ * vi_ntt_forward_padded: dst (m, n) = forward NTT of each src row (k_in <= n values) extended
+ *   with zeros; out of place, no padded copy; scratch as vi_ntt_scratch_bytes(m, n).
+ * vi_product_colsum: out[j] (+)= sum_{i<T} w[i] * EA[ia[i]*n + j] * EB[ib[i]*n + j] for j < n;
+ *   ia / ib (device int64, may be null = identity) select rows of the transformed matrices, so
+ *   a row used by several constraints is transformed once; w (device, may be null = ones);
+ *   accumulate != 0 adds into out.  scratch: vi_product_colsum_scratch_bytes(T, n). */
+int vi_ntt_forward_padded(const uint64_t* src, int64_t m, int64_t k_in, uint64_t* dst, int64_t n,
+                          void* scratch, int64_t scratch_bytes, void* stream);
+int64_t vi_product_colsum_scratch_bytes(int64_t T, int64_t n);
+int vi_product_colsum(const uint64_t* EA, const uint64_t* EB, int64_t n,
+                      const int64_t* ia_dev, const int64_t* ib_dev, const uint64_t* w_dev, int64_t T,
+                      uint64_t* out, int accumulate, void* scratch, int64_t scratch_bytes, void* stream);
+
 /* ---- Column openings ----------------------------------------------------------------
  * vi_open_columns replaces `codes.index_select(1, Q_set)` + per-column clone/cat
  * (prover/core.py:1304-1320): out[t*out_stride + row0 + r] = mat[r*n + cols[t]] for r < m,

@@ -35,6 +35,8 @@ def lib():
             getattr(L, name).argtypes = [u64, u64]
         L.or_gl_inv.restype = u64; L.or_gl_inv.argtypes = [u64]
         L.or_root_of_unity.restype = u64; L.or_root_of_unity.argtypes = [u64]
+        L.or_fold_products_eval.argtypes = [p, i64, p, i64, i64, p, p, p, i64, i64, p]
+        L.or_fold_products_eval.restype = None
         L.or_gl_matmul.argtypes = [p, p, p, i64, i64, i64]; L.or_gl_matmul.restype = None
         L.or_ntt.argtypes = [p, i64, C.c_int]; L.or_ntt.restype = None
         L.or_ntt_batched.argtypes = [p, i64, i64, C.c_int]; L.or_ntt_batched.restype = None
@@ -114,6 +116,25 @@ def encode_rows(padded, n_lig, want_polys=True, want_codes=True):
                          _ptr(polys) if want_polys else None,
                          _ptr(codes) if want_codes else None)
     return polys, codes
+
+
+def fold_products_eval(A, B, n_eval, weights=None, ia=None, ib=None):
+    """sum_i w[i] * NTT(A[ia[i]] | 0) * NTT(B[ib[i]] | 0) in the n_eval-point domain."""
+    A, B = _u64(A), _u64(B)
+    k = A.shape[1]
+    assert B.shape[1] == k
+    if ia is not None:
+        ia = np.ascontiguousarray(np.asarray(ia, dtype=np.int64))
+        ib = np.ascontiguousarray(np.asarray(ib, dtype=np.int64))
+        T = ia.size
+    else:
+        T = A.shape[0]
+    w = None if weights is None else _u64(weights)
+    out = np.empty(n_eval, dtype=np.uint64)
+    lib().or_fold_products_eval(_ptr(A), A.shape[0], _ptr(B), B.shape[0], k,
+                                None if ia is None else _ptr(ia), None if ib is None else _ptr(ib),
+                                None if w is None else _ptr(w), T, n_eval, _ptr(out))
+    return out
 
 
 # ---- hashing -----------------------------------------------------------

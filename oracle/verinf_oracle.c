@@ -138,6 +138,33 @@ void or_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int invert) {
     free(tw);
 }
 
+/* Evaluation-domain fold of row products: out[j] = sum_i w[i] * NTT_n(A_i|0)[j] * NTT_n(B_i|0)[j],
+ * rows selected by ia/ib (NULL = identity), w NULL = ones.  Follows the fused branch of
+ * _compute_q_lin_inner_chunk (prover/core.py:1892-1911) and the per-chunk weighted_eval of
+ * compute_p_0_streaming (prover/core.py:2166-2181). */
+void or_fold_products_eval(const uint64_t* A, int64_t rows_a, const uint64_t* B, int64_t rows_b, int64_t k,
+                           const int64_t* ia, const int64_t* ib, const uint64_t* w, int64_t T,
+                           int64_t n, uint64_t* out) {
+    uint64_t* ea = (uint64_t*)calloc((size_t)(rows_a * n), 8);
+    uint64_t* eb = (uint64_t*)calloc((size_t)(rows_b * n), 8);
+    for (int64_t r = 0; r < rows_a; ++r) memcpy(ea + r * n, A + r * k, (size_t)k * 8);
+    for (int64_t r = 0; r < rows_b; ++r) memcpy(eb + r * n, B + r * k, (size_t)k * 8);
+    or_ntt_batched(ea, rows_a, n, 0);
+    or_ntt_batched(eb, rows_b, n, 0);
+    #pragma omp parallel for schedule(static)
+    for (int64_t j = 0; j < n; ++j) {
+        uint64_t acc = 0;
+        for (int64_t i = 0; i < T; ++i) {
+            uint64_t a = ea[(ia ? ia[i] : i) * n + j], b = eb[(ib ? ib[i] : i) * n + j];
+            uint64_t t = f_mul(a, b);
+            if (w) t = f_mul(t, w[i]);
+            acc = f_add(acc, t);
+        }
+        out[j] = acc;
+    }
+    free(ea); free(eb);
+}
+
 /* ------------------------------------------------------------------ */
 /* RS encode: prover/core.py:721-743,746-802 (encode_messages /        */
 /* _coset_encode_codewords) and layergkr/gpu.py:141-203.               */

@@ -238,10 +238,54 @@ def merkle_path_vectors():
     np.savez_compressed(HERE / "merkle_path_vectors.npz", **out)
 
 
+def fold_vectors():
+    """Evaluation-domain fold of row products built from the reference's own CPU NTT and field
+    ops (goldilocks_ref.ntt / mul / add), following the data flow of the fused q_lin branch
+    (prover/core.py:1892-1911) and of compute_p_0_streaming's weighted_eval (:2166-2181):
+    zero-extend to n_eval = next_pow2(2K-1), forward NTT both factors, multiply pointwise,
+    weighted sum over the rows.  Also stores the inverse transform cut to 2K-1 coefficients and
+    checks it against schoolbook polynomial products."""
+    rng = random.Random(77)
+    out = {}
+    for name, m, K, T in (("small", 5, 16, 5), ("indexed", 6, 32, 11)):
+        n_eval = 1
+        while n_eval < 2 * K - 1:
+            n_eval <<= 1
+        A = [[rng.randrange(P) for _ in range(K)] for _ in range(m)]
+        B = [[rng.randrange(P) for _ in range(K)] for _ in range(m)]
+        w = [rng.randrange(P) for _ in range(T)]
+        ia = list(range(m)) if T == m else [rng.randrange(m) for _ in range(T)]
+        ib = list(range(m)) if T == m else [rng.randrange(m) for _ in range(T)]
+        om = gref.root_of_unity(n_eval)
+        EA = [gref.ntt(row + [0] * (n_eval - K), om) for row in A]
+        EB = [gref.ntt(row + [0] * (n_eval - K), om) for row in B]
+        ev_w = [0] * n_eval
+        ev_1 = [0] * n_eval
+        for t in range(T):
+            for j in range(n_eval):
+                pr = gref.mul(EA[ia[t]][j], EB[ib[t]][j])
+                ev_1[j] = gref.add(ev_1[j], pr)
+                ev_w[j] = gref.add(ev_w[j], gref.mul(pr, w[t]))
+        coef = gref.ntt(ev_w, om, invert=True)
+        want = [0] * n_eval
+        for t in range(T):
+            for x in range(K):
+                for y in range(K):
+                    want[x + y] = (want[x + y] + w[t] * A[ia[t]][x] * B[ib[t]][y]) % P
+        assert coef == want and coef[2 * K - 1:] == [0] * (n_eval - 2 * K + 1)
+        out[f"{name}_A"] = u64(A); out[f"{name}_B"] = u64(B); out[f"{name}_w"] = u64(w)
+        out[f"{name}_ia"] = np.array(ia, dtype=np.int64); out[f"{name}_ib"] = np.array(ib, dtype=np.int64)
+        out[f"{name}_eval_weighted"] = u64(ev_w); out[f"{name}_eval_ones"] = u64(ev_1)
+        out[f"{name}_coef"] = u64(coef[:2 * K - 1])
+    np.savez_compressed(HERE / "fold_vectors.npz", **out)
+
+
 if __name__ == "__main__":
-    if len(sys.argv) > 2 and sys.argv[2] == "merkle_paths":      # only this fixture
-        merkle_path_vectors()
+    if len(sys.argv) > 2:                                         # only the named fixtures
+        for name in sys.argv[2:]:
+            {"merkle_paths": merkle_path_vectors, "fold": fold_vectors}[name]()
         sys.exit(0)
+    fold_vectors()
     merkle_path_vectors()
     field_vectors()
     ntt_vectors()

@@ -76,6 +76,14 @@ def test_argument_validation_without_gpu(lib):
     assert L.vi_hash_stream_update(p, 8, 256, 128, p, 256, p, None) != 0
     assert L.vi_hash_columns(p, 4096, 200000, p, None, 0, None) != 0 and "scratch" in _err(lib)
     assert L.vi_challenge(p, p, 9, None, 4, p, None) != 0 and "label" in _err(lib)
+    assert L.vi_ntt_forward_padded(p, 1, 9, p, 8, None, 0, None) != 0 and "do not fit" in _err(lib)
+    assert L.vi_ntt_forward_padded(p, 1, 8, p, 12, None, 0, None) != 0 and "power of 2" in _err(lib)
+    assert L.vi_ntt_forward_padded(p, 0, 8, p, 16, None, 0, None) == 0
+    assert L.vi_ntt_forward_padded(p, 1, 8, p, 1 << 12, None, 0, None) != 0          # aliasing / scratch
+    assert L.vi_product_colsum(p, p, 16, None, None, None, 4, p, 0, None, 0, None) != 0 and "scratch" in _err(lib)
+    assert L.vi_product_colsum(p, p, 0, None, None, None, 4, p, 0, None, 0, None) == 0
+    assert L.vi_product_colsum_scratch_bytes(4, 16) == 16 * 8 and L.vi_product_colsum_scratch_bytes(0, 16) == 0
+    assert L.vi_product_colsum_scratch_bytes(4096, 32768) == 5 * 32768 * 8
     assert L.vi_open_columns(p, 4, 8, p, 2, p, 3, 0, None) != 0 and "stride" in _err(lib)
     assert L.vi_open_columns(p, -1, 8, p, 2, p, 3, 0, None) != 0
     assert L.vi_open_columns(p, 0, 8, p, 2, p, 3, 0, None) == 0

@@ -678,3 +678,79 @@ def test_stream_committer_equals_one_shot(cp, chunks):
     sib, sides = sc.paths()
     levels = oracle.merkle_levels(want_levels[0].cpu().numpy())
     assert commit.paths_as_reference(sib, sides) == [oracle.merkle_path(levels, j) for j in q]
+
+
+# ---------------------------------------------------------------- folds -------
+@pytest.mark.parametrize("name", ["small", "indexed"])
+def test_fold_golden(cp, golden, name):
+    from verinf_b200 import fold
+    g = golden.fold_vectors
+    A, B, w = dev(g[f"{name}_A"]), dev(g[f"{name}_B"]), dev(g[f"{name}_w"])
+    ia, ib = torch.from_numpy(g[f"{name}_ia"]).cuda(), torch.from_numpy(g[f"{name}_ib"]).cuda()
+    n_eval = fold.eval_size(A.size(1))
+    assert n_eval == g[f"{name}_eval_ones"].size
+    EA, EB = fold.ntt_forward_padded(A, n_eval), fold.ntt_forward_padded(B, n_eval)
+    assert np.array_equal(host(fold.product_colsum(EA, EB, w, ia, ib)), g[f"{name}_eval_weighted"])
+    assert np.array_equal(host(fold.product_colsum(EA, EB, None, ia, ib)), g[f"{name}_eval_ones"])
+    acc = fold.product_colsum(EA, EB, w, ia, ib)
+    cp.ntt_inverse(acc)
+    k2 = g[f"{name}_coef"].size
+    assert np.array_equal(host(acc)[:k2], g[f"{name}_coef"]) and not host(acc)[k2:].any()
+    if name == "small":
+        assert np.array_equal(host(fold.fold_products_eval(A, B, w)), g[f"{name}_eval_weighted"])
+
+
+@pytest.mark.parametrize("m,k", [(1, 2), (7, 64), (33, 512), (40, 1024), (9, 4096), (300, 2048), (5, 16384)])
+def test_fold_vs_oracle_and_reference_composition(cp, m, k):
+    from verinf_b200 import fold
+    rng = np.random.default_rng(m * 31 + k)
+    A, B, w = rnd_field(rng, (m, k)), rnd_field(rng, (m, k)), rnd_field(rng, m)
+    n_eval = fold.eval_size(k)
+    got = fold.fold_products_eval(dev(A), dev(B), dev(w))
+    assert np.array_equal(host(got), oracle.fold_products_eval(A, B, n_eval, w))
+    ones = fold.fold_products_eval(dev(A), dev(B))
+    assert np.array_equal(host(ones), oracle.fold_products_eval(A, B, n_eval))
+    # the reference's own sequence on the drop-in primitives (prover/core.py:1900-1911)
+    a_pad = torch.zeros((m, n_eval), dtype=torch.uint64, device="cuda"); a_pad[:, :k] = dev(A)
+    b_pad = torch.zeros((m, n_eval), dtype=torch.uint64, device="cuda"); b_pad[:, :k] = dev(B)
+    assert torch.equal(fold.ntt_forward_padded(dev(A), n_eval).view(torch.int64),
+                       (cp.ntt_forward_batched(a_pad), a_pad)[1].view(torch.int64))
+    cp.ntt_forward_batched(b_pad)
+    prod = cp.gl_mul(a_pad, b_pad)
+    ref = cp.gl_matvec(prod.view(torch.int64).T.contiguous().view(torch.uint64),
+                       torch.ones(m, dtype=torch.int64, device="cuda").view(torch.uint64))
+    assert torch.equal(ref.view(torch.int64), ones.view(torch.int64))
+    # accumulation into an existing buffer and linearity of the inverse transform
+    acc = ones.clone()
+    fold.fold_products_eval(dev(A), dev(B), dev(w), out=acc)
+    assert np.array_equal(host(acc), host(cp.gl_add(ones, got)))
+    if k <= 1024:
+        cp.ntt_inverse(ones)
+        pm = cp.poly_mul_batched(dev(A), dev(B))
+        s = host(cp.gl_matvec(pm.view(torch.int64).T.contiguous().view(torch.uint64),
+                              torch.ones(m, dtype=torch.int64, device="cuda").view(torch.uint64)))
+        assert np.array_equal(host(ones)[:2 * k - 1], s)
+
+
+def test_fold_indexed_rows_and_edges(cp):
+    from verinf_b200 import fold
+    rng = np.random.default_rng(4)
+    rows, k, T = 50, 256, 700
+    A, B, w = rnd_field(rng, (rows, k)), rnd_field(rng, (rows + 3, k)), rnd_field(rng, T)
+    ia, ib = rng.integers(0, rows, size=T), rng.integers(0, rows + 3, size=T)
+    n_eval = fold.eval_size(k)
+    EA, EB = fold.ntt_forward_padded(dev(A), n_eval), fold.ntt_forward_padded(dev(B), n_eval)
+    got = fold.product_colsum(EA, EB, dev(w), torch.from_numpy(ia).cuda(), torch.from_numpy(ib).cuda())
+    assert np.array_equal(host(got), oracle.fold_products_eval(A, B, n_eval, w, ia, ib))
+    # largest operands: every product and the carry limb at their bounds
+    big = torch.full((600, 512), -(1 << 32), dtype=torch.int64, device="cuda").view(torch.uint64)   # p - 1
+    s = fold.product_colsum(big, big)
+    assert host(s).tolist() == [600 % P] * 512
+    e = torch.empty((0, 512), dtype=torch.uint64, device="cuda")
+    assert not host(fold.product_colsum(e, e)).any()
+    with pytest.raises(RuntimeError):
+        fold.product_colsum(EA, EB)                         # row counts differ and no indices
+    with pytest.raises(RuntimeError):
+        fold.product_colsum(EA, EB, None, torch.tensor([rows], device="cuda"), torch.tensor([0], device="cuda"))
+    with pytest.raises(RuntimeError):
+        fold.ntt_forward_padded(dev(A), 128)                # rows longer than the transform

@@ -134,3 +134,16 @@ def test_matmul_against_python_integers():
     for i in range(5):
         for j in range(4):
             assert int(got[i, j]) == sum(int(A[i, l]) * int(B[l, j]) for l in range(37)) % P
+
+
+@pytest.mark.parametrize("name", ["small", "indexed"])
+def test_fold_vectors(golden, name):
+    g = golden.fold_vectors
+    A, B, w, ia, ib = (g[f"{name}_{k}"] for k in ("A", "B", "w", "ia", "ib"))
+    n_eval = g[f"{name}_eval_ones"].size
+    assert np.array_equal(oracle.fold_products_eval(A, B, n_eval, w, ia, ib), g[f"{name}_eval_weighted"])
+    assert np.array_equal(oracle.fold_products_eval(A, B, n_eval, None, ia, ib), g[f"{name}_eval_ones"])
+    coef = oracle.ntt(oracle.fold_products_eval(A, B, n_eval, w, ia, ib), invert=True)
+    assert np.array_equal(coef[:g[f"{name}_coef"].size], g[f"{name}_coef"]) and not coef[g[f"{name}_coef"].size:].any()
+    if name == "small":
+        assert np.array_equal(oracle.fold_products_eval(A, B, n_eval, w), g[f"{name}_eval_weighted"])

@@ -67,20 +67,22 @@ __global__ void k_poly_eval(const uint64_t* __restrict__ coeffs, int64_t m, int6
 }
 
 // C = A.B mod p with lazily reduced accumulation.
-// CTA tile 64 x 32 outputs, k in slices of 32, 256 threads, 4 x 2 outputs per thread.  Each
-// 64 x 64 -> 128-bit product is never formed: a is split into two 32-bit limbs, b into limbs of
-// 22 + 22 + 20 bits, and the six limb products (< 2^54) are summed in six 64-bit accumulators by
-// one wide multiply-add each (FMA pipe, no carry chain).  1024 products fit before an
-// accumulator could overflow, so every 32 slices (and at the end) the six sums are recombined
-// sum_ij acc_ij * 2^(32 i + 22 j), reduced mod p and added into C.  Tiles arrive through
-// cp.async into a double buffer when they are whole and 16-byte aligned, else through guarded
-// loads with zero fill.
+// CTA tile 64 x 32 outputs, k in slices of 32, 256 threads, 4 x 2 outputs per thread.  The
+// 128-bit products are summed unreduced in five 32-bit limbs per output (8 multiply-adds with
+// carry on the FMA pipe + 5 carry propagations on the ALU pipe per product, no modular
+// reduction); the fifth limb counts the carries out of 2^128, so any k < 2^32 fits, and the
+// 160-bit sum is reduced mod p once at the end (2^128 = -2^32).  Tiles arrive through cp.async into a
+// double buffer when they are whole and 16-byte aligned, else through guarded loads with zero
+// fill.  Measured on B200 (1000 x 4096 x 11008): 41 ms = 1.09 T multiply-adds/s, the heavy half
+// of the FMA pipe 93 % busy (32-bit multiply-adds issue at 4 clocks per warp there); summing
+// 22-bit-limb products with wide multiply-adds instead (no carries) took 50 ms because a wide
+// multiply-add with a 64-bit addend is not one instruction on this architecture, and the
+// reduce-every-product kernel this replaces 68 ms.
 #ifndef VI_MM_MINB
 #define VI_MM_MINB 2      // resident CTAs per SM asked of the compiler (128 registers per thread)
 #endif
 constexpr int MM_TM = 64, MM_TN = 32, MM_TK = 32, MM_AS = 34;   // MM_AS: row stride of the A tile (u64)
 constexpr int MM_SMEM = 2 * (MM_TM * MM_AS + MM_TK * MM_TN) * 8;
-constexpr int MM_FLUSH = 32;                                      // slices between reductions
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
@@ -89,14 +91,6 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// acc * 2^S mod p for any 64-bit acc, S < 128
-template <int S>
-__device__ __forceinline__ uint64_t shifted_mod(uint64_t acc) {
-    if constexpr (S == 0) return vgl::reduce128(acc, 0);
-    else if constexpr (S < 64) return vgl::reduce128(acc << S, acc >> (64 - S));
-    else return vgl::reduce128(0, shifted_mod<S - 64>(acc));
-}
 
 __global__ void __launch_bounds__(256, VI_MM_MINB) k_matmul(const uint64_t* __restrict__ A, const uint64_t* __restrict__ B,
                                                    uint64_t* __restrict__ C, int64_t m, int64_t k, int64_t n) {
@@ -143,13 +137,14 @@ __global__ void __launch_bounds__(256, VI_MM_MINB) k_matmul(const uint64_t* __re
         cp_async_commit();
     };
 
-    uint64_t acc[4][2][6];
+    uint32_t acc[4][2][5];
 #pragma unroll
     for (int q = 0; q < 4; ++q)
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int t = 0; t < 6; ++t) acc[q][c][t] = 0;
+            for (int t = 0; t < 5; ++t) acc[q][c][t] = 0;
+
     if (nslices > 0) load_slice(0, 0);
     for (int64_t s = 0; s < nslices; ++s) {
         const int buf = (int)(s & 1);
@@ -162,56 +157,92 @@ __global__ void __launch_bounds__(256, VI_MM_MINB) k_matmul(const uint64_t* __re
         for (int l = 0; l < MM_TK; ++l) {
             const uint4 bb = *reinterpret_cast<const uint4*>(sb + l * MM_TN + 2 * tx);
             const uint64_t bv[2] = {vgl::pack(bb.x, bb.y), vgl::pack(bb.z, bb.w)};
-            uint32_t bl[2][3];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                bl[c][0] = (uint32_t)bv[c] & 0x3FFFFFu;
-                bl[c][1] = (uint32_t)(bv[c] >> 22) & 0x3FFFFFu;
-                bl[c][2] = (uint32_t)(bv[c] >> 44);
-            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint64_t av = sa[(ty * 4 + q) * MM_AS + l];
                 const uint32_t a0 = (uint32_t)av, a1 = (uint32_t)(av >> 32);
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int j = 0; j < 3; ++j) {
-                        acc[q][c][j] += (uint64_t)a0 * bl[c][j];
-                        acc[q][c][3 + j] += (uint64_t)a1 * bl[c][j];
-                    }
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t* x = acc[q][c];
+                    const uint32_t b0 = (uint32_t)bv[c], b1 = (uint32_t)(bv[c] >> 32);
+                    asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
+                        "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
+                        "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
+                        "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
+                        "addc.u32 %4, %4, 0;\n\t"
+                        "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
+                        "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
+                        "addc.cc.u32 %3, %3, 0;\n\t"
+                        "addc.u32 %4, %4, 0;\n\t"
+                        "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
+                        "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
+                        "addc.cc.u32 %3, %3, 0;\n\t"
+                        "addc.u32 %4, %4, 0;"
+                        : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4])
+                        : "r"(a0), "r"(a1), "r"(b0), "r"(b1));
+                }
             }
         }
         __syncthreads();
-        if ((s + 1) % MM_FLUSH == 0 || s + 1 == nslices) {
-            const bool first = s < MM_FLUSH;           // nothing has been written to C yet
+    }
+    // x4*2^128 + (x3:x2)*2^64 + (x1:x0) mod p, with 2^128 = -2^32; x4 < k < 2^32, so x4 << 32 <= p - 1
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
+    for (int q = 0; q < 4; ++q)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint64_t* a6 = acc[q][c];
-                    uint64_t v = shifted_mod<0>(a6[0]);
-                    v = add(v, shifted_mod<22>(a6[1]));
-                    v = add(v, shifted_mod<44>(a6[2]));
-                    v = add(v, shifted_mod<32>(a6[3]));
-                    v = add(v, shifted_mod<54>(a6[4]));
-                    v = add(v, shifted_mod<76>(a6[5]));
-                    const int64_t r = row0 + ty * 4 + q, cc = col0 + 2 * tx + c;
-                    if (r < m && cc < n) C[r * n + cc] = first ? v : add(C[r * n + cc], v);
-#pragma unroll
-                    for (int t = 0; t < 6; ++t) a6[t] = 0;
-                }
+        for (int c = 0; c < 2; ++c) {
+            const uint32_t* x = acc[q][c];
+            const uint64_t v = vgl::sub(vgl::reduce128(vgl::pack(x[0], x[1]), vgl::pack(x[2], x[3])), (uint64_t)x[4] << 32);
+            const int64_t r = row0 + ty * 4 + q, cc = col0 + 2 * tx + c;
+            if (r < m && cc < n) C[r * n + cc] = v;
         }
+}
+
+// Weighted product column sum: part[s][j] = sum over the rows i of split s of
+// w[i] * EA[ia[i]][j] * EB[ib[i]][j].  One thread per column (coalesced rows), products summed
+// unreduced in five 32-bit limbs, one reduction per thread at the end; k_colsum_finish adds the
+// row splits (and the previous value when accumulating).
+__global__ void __launch_bounds__(256) k_product_colsum(const uint64_t* __restrict__ EA, const uint64_t* __restrict__ EB,
+                                                        int64_t n, const int64_t* __restrict__ ia,
+                                                        const int64_t* __restrict__ ib, const uint64_t* __restrict__ w,
+                                                        int64_t T, int64_t rows_per_split, uint64_t* __restrict__ part) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const int64_t i0 = (int64_t)blockIdx.y * rows_per_split;
+    const int64_t i1 = i0 + rows_per_split < T ? i0 + rows_per_split : T;
+    uint32_t x0 = 0, x1 = 0, x2 = 0, x3 = 0, x4 = 0;
+    for (int64_t i = i0; i < i1; ++i) {
+        const int64_t ra = ia ? __ldg(ia + i) : i, rb = ib ? __ldg(ib + i) : i;
+        uint64_t a = EA[ra * n + j];
+        const uint64_t b = EB[rb * n + j];
+        if (w) a = mul(a, __ldg(w + i));
+        const uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
+        asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
+            "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
+            "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
+            "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
+            "addc.u32 %4, %4, 0;\n\t"
+            "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
+            "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
+            "addc.cc.u32 %3, %3, 0;\n\t"
+            "addc.u32 %4, %4, 0;\n\t"
+            "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
+            "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
+            "addc.cc.u32 %3, %3, 0;\n\t"
+            "addc.u32 %4, %4, 0;"
+            : "+r"(x0), "+r"(x1), "+r"(x2), "+r"(x3), "+r"(x4)
+            : "r"(a0), "r"(a1), "r"(b0), "r"(b1));
     }
-    if (nslices == 0) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int64_t r = row0 + ty * 4 + q, cc = col0 + 2 * tx + c;
-                if (r < m && cc < n) C[r * n + cc] = 0;
-            }
-    }
+    part[(int64_t)blockIdx.y * n + j] =
+        vgl::sub(vgl::reduce128(vgl::pack(x0, x1), vgl::pack(x2, x3)), (uint64_t)x4 << 32);
+}
+
+__global__ void __launch_bounds__(256) k_colsum_finish(const uint64_t* __restrict__ part, int splits, int64_t n,
+                                                       uint64_t* __restrict__ out, int accumulate) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    uint64_t v = accumulate ? out[j] : 0;
+    for (int s = 0; s < splits; ++s) v = add(v, part[(int64_t)s * n + j]);
+    out[j] = v;
 }
 
 // w = M.v: one warp per row, lanes stride the row, shuffle reduction.
@@ -402,6 +433,7 @@ extern "C" int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, i
     if (m == 0 || n == 0) return VI_OK;
     VI_REQUIRE(A && B && C || k == 0, "gl_matmul: null pointer");
     VI_REQUIRE(C != A && C != B, "gl_matmul: the output must not alias an input");
+    VI_REQUIRE(k < (int64_t(1) << 32), "gl_matmul: inner dimension must be below 2^32");
     dim3 grid((unsigned)((n + MM_TN - 1) / MM_TN), (unsigned)((m + MM_TM - 1) / MM_TM));
     VI_REQUIRE(grid.y <= 65535, "gl_matmul: too many rows for one launch (m <= 4194240)");
     VI_CUDA(cudaFuncSetAttribute(k_matmul, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM));
@@ -455,4 +487,50 @@ extern "C" int vi_interp_band(int kind, uint64_t* out, int64_t out_off, int64_t 
     VI_REQUIRE(grid <= 0x7FFFFFFFLL, "interp_band: too many slots");
     k_band<<<(unsigned)grid, BLOCK, 0, (cudaStream_t)stream>>>(a);
     return vi::check_launch("k_band");
+}
+
+namespace {
+int colsum_splits(int64_t T, int64_t n) {
+    // enough CTAs for ~4 per SM, at least 8 rows per split
+    int64_t col_blocks = (n + 255) / 256;
+    int64_t want = (148 * 4 + col_blocks - 1) / col_blocks;
+    int64_t max_by_rows = (T + 7) / 8;
+    int64_t s = want < max_by_rows ? want : max_by_rows;
+    if (s < 1) s = 1;
+    if (s > 1024) s = 1024;
+    return (int)s;
+}
+}  // namespace
+
+extern "C" int64_t vi_product_colsum_scratch_bytes(int64_t T, int64_t n) {
+    if (T <= 0 || n <= 0) return 0;
+    return (int64_t)colsum_splits(T, n) * n * 8;
+}
+
+extern "C" int vi_product_colsum(const uint64_t* EA, const uint64_t* EB, int64_t n,
+                                 const int64_t* ia_dev, const int64_t* ib_dev, const uint64_t* w_dev, int64_t T,
+                                 uint64_t* out, int accumulate, void* scratch, int64_t scratch_bytes, void* stream) {
+    VI_REQUIRE(T >= 0 && n >= 0, "product_colsum: negative size");
+    if (n == 0) return VI_OK;
+    VI_REQUIRE(out != nullptr, "product_colsum: null output");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (T == 0) {
+        if (!accumulate) VI_CUDA(cudaMemsetAsync(out, 0, (size_t)n * 8, st));
+        return VI_OK;
+    }
+    VI_REQUIRE(EA && EB, "product_colsum: null input");
+    VI_REQUIRE(T < (int64_t(1) << 32), "product_colsum: too many rows");
+    const int splits = colsum_splits(T, n);
+    if (scratch == nullptr || scratch_bytes < (int64_t)splits * n * 8)
+        return vi::fail(VI_ERR_SCRATCH, "product_colsum: scratch of at least %lld bytes required (see vi_product_colsum_scratch_bytes)",
+                        (long long)((int64_t)splits * n * 8));
+    const int64_t per = (T + splits - 1) / splits;
+    const int64_t gx = (n + 255) / 256;
+    if (gx > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "product_colsum: too many columns");
+    dim3 grid((unsigned)gx, (unsigned)splits);
+    k_product_colsum<<<grid, 256, 0, st>>>(EA, EB, n, ia_dev, ib_dev, w_dev, T, per, (uint64_t*)scratch);
+    int rc = vi::check_launch("k_product_colsum");
+    if (rc) return rc;
+    k_colsum_finish<<<(unsigned)gx, 256, 0, st>>>((const uint64_t*)scratch, splits, n, out, accumulate);
+    return vi::check_launch("k_colsum_finish");
 }

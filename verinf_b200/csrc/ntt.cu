@@ -590,6 +590,60 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
     return VI_OK;
 }
 
+// dst (m, n) = forward NTT of each src row (k_in values) extended with zeros to length n.
+// Above the single-pass length the zero extension costs nothing: the first pass reads through
+// the message loader, which returns zero past k_in; no padded copy of the input is written.
+extern "C" int vi_ntt_forward_padded(const uint64_t* src, int64_t m, int64_t k_in, uint64_t* dst, int64_t n,
+                                     void* scratch, int64_t scratch_bytes, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    VI_REQUIRE(m >= 0 && k_in >= 0, "ntt_forward_padded: negative size");
+    VI_REQUIRE(vi::is_pow2(n) && n >= 2, "NTT length must be a power of 2 >= 2 (got %lld)", (long long)n);
+    VI_REQUIRE(k_in <= n, "ntt_forward_padded: rows of %lld values do not fit length %lld", (long long)k_in, (long long)n);
+    const int logn = vi::ilog2(n);
+    if (logn > 2 * MAX_LOGL) return vi::fail(VI_ERR_LIMIT, "NTT length 2^%d exceeds the supported 2^%d", logn, 2 * MAX_LOGL);
+    if (m == 0) return VI_OK;
+    VI_REQUIRE(dst != nullptr && (src != nullptr || k_in == 0), "ntt_forward_padded: null pointer");
+    VI_REQUIRE(dst != src, "ntt_forward_padded: output must not alias the input");
+    if (logn <= SINGLE_LOGL) {
+        if (k_in < n) VI_CUDA(cudaMemsetAsync(dst, 0, (size_t)(m * n) * 8, st));
+        if (k_in > 0)
+            VI_CUDA(cudaMemcpy2DAsync(dst, (size_t)n * 8, src, (size_t)k_in * 8, (size_t)k_in * 8, (size_t)m,
+                                      cudaMemcpyDeviceToDevice, st));
+        return vi_ntt_batched(dst, m, n, 0, nullptr, 0, stream);
+    }
+    const int log1 = (logn + 1) / 2, log2 = logn - log1;
+    const int64_t n1 = int64_t(1) << log1, n2 = int64_t(1) << log2;
+    VI_REQUIRE(scratch != nullptr && scratch_bytes >= n * 8,
+               "ntt: scratch of at least %lld bytes required (see vi_ntt_scratch_bytes)", (long long)(n * 8));
+    const int64_t chunk = scratch_bytes / (n * 8);
+    const uint64_t* fsn;
+    int rc = get_fs(n, n2, false, &fsn);
+    if (rc) return rc;
+    for (int64_t r0 = 0; r0 < m; r0 += chunk) {
+        const int64_t cnt = m - r0 < chunk ? m - r0 : chunk;
+        PassArgs a{};
+        a.in = src + r0 * k_in; a.out = (uint64_t*)scratch;
+        a.logC = pick_logC(log1, n2);
+        a.ncols = n2;
+        a.in_item = k_in; a.in_idx = (uint32_t)n2; a.in_col = 1;
+        a.out_item = n; a.out_k = (uint32_t)n2; a.out_col = 1;
+        a.fs = fsn; a.scale = 1; a.out_via_smem = 0;
+        a.src_kind = SRC_MSG; a.ell = k_in; a.pad_mode = 0;
+        rc = launch_pass(log1, false, 0, a, cnt, st, vi::PROF_NTT_PASS);
+        if (rc) return rc;
+        PassArgs b{};
+        b.in = (const uint64_t*)scratch; b.out = dst + r0 * n;
+        b.logC = pick_logC(log2, n1);
+        b.ncols = n1;
+        b.in_item = n; b.in_idx = 1; b.in_col = (uint32_t)n2;
+        b.out_item = n; b.out_k = (uint32_t)n1; b.out_col = 1;
+        b.fs = nullptr; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
+        rc = launch_pass(log2, false, 1, b, cnt, st, vi::PROF_NTT_PASS);
+        if (rc) return rc;
+    }
+    return VI_OK;
+}
+
 extern "C" int64_t vi_encode_scratch_bytes(int64_t m, int64_t k, int64_t n) {
     if (m <= 0) return 0;
     int64_t row = (k + n) * 8;
