@@ -66,6 +66,31 @@ __global__ void k_poly_eval(const uint64_t* __restrict__ coeffs, int64_t m, int6
     out[r * k + p] = acc;
 }
 
+// (x4:x3:x2:x1:x0) += a * b as integers: 8 multiply-adds with carry + 5 carry propagations,
+// no modular reduction.  x4 counts the carries out of 2^128, so 2^32 products fit.
+__device__ __forceinline__ void mac160(uint32_t (&x)[5], uint64_t a, uint64_t b) {
+    const uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
+    asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
+        "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
+        "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
+        "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
+        "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
+        "addc.cc.u32 %3, %3, 0;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
+        "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
+        "addc.cc.u32 %3, %3, 0;\n\t"
+        "addc.u32 %4, %4, 0;"
+        : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(b1));
+}
+// the 160-bit sum mod p: 2^128 = -2^32 (mod p), and x4 << 32 <= p - 1 is canonical
+__device__ __forceinline__ uint64_t reduce160(const uint32_t (&x)[5]) {
+    return vgl::sub(vgl::reduce128(vgl::pack(x[0], x[1]), vgl::pack(x[2], x[3])), (uint64_t)x[4] << 32);
+}
+
 // C = A.B mod p with lazily reduced accumulation.
 // CTA tile 64 x 32 outputs, k in slices of 32, 256 threads, 4 x 2 outputs per thread.  The
 // 128-bit products are summed unreduced in five 32-bit limbs per output (8 multiply-adds with
@@ -160,40 +185,18 @@ __global__ void __launch_bounds__(256, VI_MM_MINB) k_matmul(const uint64_t* __re
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint64_t av = sa[(ty * 4 + q) * MM_AS + l];
-                const uint32_t a0 = (uint32_t)av, a1 = (uint32_t)(av >> 32);
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t* x = acc[q][c];
-                    const uint32_t b0 = (uint32_t)bv[c], b1 = (uint32_t)(bv[c] >> 32);
-                    asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
-                        "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
-                        "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
-                        "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
-                        "addc.u32 %4, %4, 0;\n\t"
-                        "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
-                        "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
-                        "addc.cc.u32 %3, %3, 0;\n\t"
-                        "addc.u32 %4, %4, 0;\n\t"
-                        "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
-                        "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
-                        "addc.cc.u32 %3, %3, 0;\n\t"
-                        "addc.u32 %4, %4, 0;"
-                        : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4])
-                        : "r"(a0), "r"(a1), "r"(b0), "r"(b1));
-                }
+                for (int c = 0; c < 2; ++c) mac160(acc[q][c], av, bv[c]);
             }
         }
         __syncthreads();
     }
-    // x4*2^128 + (x3:x2)*2^64 + (x1:x0) mod p, with 2^128 = -2^32; x4 < k < 2^32, so x4 << 32 <= p - 1
 #pragma unroll
     for (int q = 0; q < 4; ++q)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-            const uint32_t* x = acc[q][c];
-            const uint64_t v = vgl::sub(vgl::reduce128(vgl::pack(x[0], x[1]), vgl::pack(x[2], x[3])), (uint64_t)x[4] << 32);
             const int64_t r = row0 + ty * 4 + q, cc = col0 + 2 * tx + c;
-            if (r < m && cc < n) C[r * n + cc] = v;
+            if (r < m && cc < n) C[r * n + cc] = reduce160(acc[q][c]);
         }
 }
 
@@ -209,31 +212,15 @@ __global__ void __launch_bounds__(256) k_product_colsum(const uint64_t* __restri
     if (j >= n) return;
     const int64_t i0 = (int64_t)blockIdx.y * rows_per_split;
     const int64_t i1 = i0 + rows_per_split < T ? i0 + rows_per_split : T;
-    uint32_t x0 = 0, x1 = 0, x2 = 0, x3 = 0, x4 = 0;
+    uint32_t x[5] = {0, 0, 0, 0, 0};
     for (int64_t i = i0; i < i1; ++i) {
         const int64_t ra = ia ? __ldg(ia + i) : i, rb = ib ? __ldg(ib + i) : i;
         uint64_t a = EA[ra * n + j];
         const uint64_t b = EB[rb * n + j];
         if (w) a = mul(a, __ldg(w + i));
-        const uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
-        asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
-            "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
-            "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
-            "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
-            "addc.u32 %4, %4, 0;\n\t"
-            "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
-            "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
-            "addc.cc.u32 %3, %3, 0;\n\t"
-            "addc.u32 %4, %4, 0;\n\t"
-            "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
-            "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
-            "addc.cc.u32 %3, %3, 0;\n\t"
-            "addc.u32 %4, %4, 0;"
-            : "+r"(x0), "+r"(x1), "+r"(x2), "+r"(x3), "+r"(x4)
-            : "r"(a0), "r"(a1), "r"(b0), "r"(b1));
+        mac160(x, a, b);
     }
-    part[(int64_t)blockIdx.y * n + j] =
-        vgl::sub(vgl::reduce128(vgl::pack(x0, x1), vgl::pack(x2, x3)), (uint64_t)x4 << 32);
+    part[(int64_t)blockIdx.y * n + j] = reduce160(x);
 }
 
 __global__ void __launch_bounds__(256) k_colsum_finish(const uint64_t* __restrict__ part, int splits, int64_t n,
@@ -245,15 +232,16 @@ __global__ void __launch_bounds__(256) k_colsum_finish(const uint64_t* __restric
     out[j] = v;
 }
 
-// w = M.v: one warp per row, lanes stride the row, shuffle reduction.
+// w = M.v: one warp per row, lanes stride the row summing unreduced products, shuffle reduction.
 __global__ void __launch_bounds__(256) k_matvec(const uint64_t* __restrict__ M, const uint64_t* __restrict__ v,
                                                 uint64_t* __restrict__ w, int64_t m, int64_t n) {
     const int lane = threadIdx.x & 31;
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (row >= m) return;
     const uint64_t* r = M + row * n;
-    uint64_t acc = 0;
-    for (int64_t j = lane; j < n; j += 32) acc = add(acc, mul(r[j], __ldg(v + j)));
+    uint32_t x[5] = {0, 0, 0, 0, 0};
+    for (int64_t j = lane; j < n; j += 32) mac160(x, r[j], __ldg(v + j));
+    uint64_t acc = reduce160(x);
 #pragma unroll
     for (int o = 16; o; o >>= 1) acc = add(acc, __shfl_xor_sync(0xffffffffu, acc, o));
     if (lane == 0) w[row] = acc;
