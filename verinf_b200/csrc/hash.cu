@@ -123,6 +123,33 @@ __global__ void __launch_bounds__(128) k_merkle_level(const uint32_t* __restrict
     for (int k = 0; k < 8; ++k) out[i * 8 + k] = h[k];
 }
 
+// All levels above a level of at most MERKLE_TOP_NODES nodes in one single-CTA launch (a level per
+// loop iteration, block barrier in between) instead of one launch per level: the upper eleven
+// levels of a tree are launch latency only.  Loads are plain (not read-only-cache) loads because
+// each level reads what the previous iteration of the same kernel wrote.
+constexpr int MERKLE_TOP_NODES = 2048;
+__global__ void __launch_bounds__(512) k_merkle_top(const uint32_t* in, int64_t n_in, uint32_t* out) {
+    const uint32_t* cur = in;
+    uint32_t* nxt = out;
+    int64_t n = n_in;
+    while (n > 1) {
+        const int64_t n_out = (n + 1) >> 1;
+        for (int64_t i = threadIdx.x; i < n_out; i += blockDim.x) {
+            const int64_t li = 2 * i, ri = (2 * i + 1 < n) ? 2 * i + 1 : 2 * i;
+            uint32_t m[16], h[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { m[k] = cur[li * 8 + k]; m[8 + k] = cur[ri * 8 + k]; }
+            vb3::hash_one_block(m, 64, h);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) nxt[i * 8 + k] = h[k];
+        }
+        __syncthreads();
+        cur = nxt;
+        nxt += n_out * 8;
+        n = n_out;
+    }
+}
+
 __global__ void __launch_bounds__(256) k_row_prg(const uint8_t* __restrict__ seed, int64_t row_off,
                                                  const uint64_t* __restrict__ rows, int64_t n_rows,
                                                  int64_t slack, uint64_t* __restrict__ out) {
@@ -413,12 +440,18 @@ extern "C" int vi_merkle_build(const uint8_t* leaves, int64_t n, uint8_t* upper,
     VI_REQUIRE(n >= 0, "merkle: negative size");
     const uint8_t* cur = leaves;
     uint8_t* nxt = upper;
-    while (n > 1) {
+    while (n > MERKLE_TOP_NODES) {
         int rc = vi_merkle_level(cur, n, nxt, stream);
         if (rc) return rc;
         n = (n + 1) / 2;
         cur = nxt;
         nxt += n * 32;
+    }
+    if (n > 1) {
+        VI_REQUIRE(cur != nullptr && nxt != nullptr, "merkle: null pointer");
+        vi::ProfScope prof(vi::PROF_MERKLE, (cudaStream_t)stream);
+        k_merkle_top<<<1, 512, 0, (cudaStream_t)stream>>>((const uint32_t*)cur, n, (uint32_t*)nxt);
+        return vi::check_launch("k_merkle_top");
     }
     return VI_OK;
 }

@@ -135,8 +135,10 @@ def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
             fa = torch.zeros(width, dtype=torch.int64, device=dev); fa[:n_in] = a.view(torch.int64)
             fb = torch.zeros(width, dtype=torch.int64, device=dev); fb[:n_in] = b.view(torch.int64)
             coins = [((i + 1) * 0x9E3779B97F4A7C15 + 7) % P for i in range(width.bit_length() - 1)]
+            # the challenges of a layergkr sumcheck are drawn before it starts
+            # (layergkr/full_layer.py:222 `coins = tr.coin(f"sc_{m.name}", n)`), so all rounds are queued at once
             claim, polys, _, _ = lg.prove_terms_gpu([(1, [fa.view(torch.uint64), fb.view(torch.uint64)])],
-                                                    lambda i: coins[i])
+                                                    lambda i: coins[i], coins=coins)
             yt = cp.gl_matvec(Y[name], tau)                                                           # Y tau (seq)
             want = int(cp.gl_matvec(yt.reshape(1, -1), rho)[0].item())                                # rho^T Y tau
             ok = ok and claim == want and (polys[0][0][1] + polys[0][1][1]) % P == claim
