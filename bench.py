@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--sumcheck", action="store_true", help="also time the 2^24 degree-3 sumcheck")
     ap.add_argument("--extra", action="store_true",
                     help="also run the secondary workloads: fused K-quant lift+encode, 7B-layer commit+sumcheck")
+    ap.add_argument("--micro", choices=["matmul", "fold"],
+                    help="run only a small case of one secondary kernel (1024 x 2048 x 2048 matmul, or the fold "
+                         "of 1024 row pairs at K = 16384) and print its figures; the case the ncu summaries use")
     return ap.parse_args()
 
 
@@ -251,6 +254,8 @@ def run_native(a):
         torch.cuda.empty_cache()
         extra["kquant_fused_encode"] = [workloads.kquant_fused_encode(dev, q) for q in ("Q4_K", "Q6_K")]
         extra["layer7b"] = workloads.layer7b_commit_sumcheck(dev)
+        extra["field_matmul"] = workloads.field_matmul(dev)
+        extra["fold_products"] = workloads.fold_products(dev)
 
     if rank == 0:
         elems = world * rows * n
@@ -341,9 +346,20 @@ def time_sumcheck(torch, dev):
     return {"ms": best * 1e3, "algorithmic_gbs": nbytes / best / 1e9}
 
 
+def run_micro(a):
+    import torch
+    from verinf_b200 import workloads
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    out = workloads.field_matmul(dev, 1024, 2048, 2048) if a.micro == "matmul" else workloads.fold_products(dev)
+    print(json.dumps({"micro": a.micro, **out}))
+
+
 if __name__ == "__main__":
     args = parse()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_native(args)

@@ -90,6 +90,56 @@ def kquant_fused_encode(dev, qtype="Q4_K", seed=3):
             "codeword_gbs": rows * N_LIG * 8 / t_fus / 1e9}
 
 
+def _event_ms(fn, reps=5, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def field_matmul(dev, m=1000, k=4096, n=11008, seed=5):
+    """Witness matmul Y = X W mod p of one MLP projection (gl_matmul, prover/cuda_primitives.py:1086-1106)."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    X = _rand_int8_field((m, k), g, dev)
+    W = _rand_int8_field((k, n), g, dev)
+    ms = _event_ms(lambda: cp.gl_matmul(X, W))
+    return {"m": m, "k": k, "n": n, "ms": ms, "multiply_adds_per_s": m * k * n / ms * 1e3}
+
+
+def fold_products(dev, rows=1024, k_deg=K_DEG, seed=9):
+    """Evaluation-domain fold of `rows` pairs of degree-<K polynomials (the q_lin / p_0 transform,
+    prover/core.py:1892-1911): the fused path against the reference's sequence on the same kernels."""
+    from . import fold
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    A = torch.randint(0, 1 << 62, (rows, k_deg), dtype=torch.int64, device=dev, generator=g).view(torch.uint64)
+    B = torch.randint(0, 1 << 62, (rows, k_deg), dtype=torch.int64, device=dev, generator=g).view(torch.uint64)
+    n_eval = fold.eval_size(k_deg)
+    ones = torch.ones(rows, dtype=torch.int64, device=dev).view(torch.uint64)
+
+    def composed():
+        a_pad = A.new_zeros((rows, n_eval)); a_pad[:, :k_deg] = A
+        b_pad = B.new_zeros((rows, n_eval)); b_pad[:, :k_deg] = B
+        cp.ntt_forward_batched(a_pad); cp.ntt_forward_batched(b_pad)
+        prod = cp.gl_mul(a_pad, b_pad)
+        return cp.gl_matvec(prod.view(torch.int64).T.contiguous().view(torch.uint64), ones)
+
+    same = bool(torch.equal(composed().view(torch.int64), fold.fold_products_eval(A, B).view(torch.int64)))
+    t_ref = _event_ms(composed)
+    t_fused = _event_ms(lambda: fold.fold_products_eval(A, B))
+    EA, EB = fold.ntt_forward_padded(A, n_eval), fold.ntt_forward_padded(B, n_eval)
+    t_sum = _event_ms(lambda: fold.product_colsum(EA, EB))
+    return {"rows": rows, "K": k_deg, "n_eval": n_eval, "bit_identical_to_composed": same, "fused_ms": t_fused,
+            "composed_ms": t_ref, "colsum_ms": t_sum, "colsum_gbs": 2 * rows * n_eval * 8 / t_sum / 1e6}
+
+
 def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
     """BASELINE config 5 (dense variant): int8 weights/activations of one Llama-2-7B-shaped layer,
     every weight and activation tensor committed (encode + column hash + Merkle), one deg-2
