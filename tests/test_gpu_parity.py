@@ -379,11 +379,12 @@ def synth_blocks(rng, qt, nb):
 
 @pytest.mark.parametrize("qt", ["Q4_K", "Q6_K"])
 @pytest.mark.parametrize("transpose", [True, False])
-def test_kquant_fused_encode(cp, qt, transpose):
+@pytest.mark.parametrize("d_out", [96, 128])
+def test_kquant_fused_encode(cp, qt, transpose, d_out):
     """fused lift+encode == kquant_to_field -> (transpose) -> row packing -> encode (with PRG pad)"""
     from verinf_b200 import kquant_cuda as kq
     rng = np.random.default_rng(23)
-    d_out, d_in, ell, k, n = 96, 512, 1000, 2048, 8192
+    d_in, ell, k, n = 512, 1000, 2048, 8192
     raw = synth_blocks(rng, qt, d_out * d_in // 256)
     S = 1 << 12
     lifted = oracle.kquant_to_field(raw, qt, S).reshape(d_out, d_in)
@@ -407,6 +408,14 @@ def test_kquant_fused_encode(cp, qt, transpose):
     p2, c2 = kq.kquant_encode_rows(torch.from_numpy(raw).cuda(), qt, S, d_out, d_in, ell=ell, k_deg=k, n_lig=n,
                                    transpose=transpose, first_row=7, n_rows=9, master_seed=seed_t, row_offset=12)
     assert p2 is None and torch.equal(c2.view(torch.int64), want_c[7:16].view(torch.int64))
+    # scratch with room for one row chunk only: no staging area, the loader decodes from the super-blocks
+    from verinf_b200._lib import LIB, check, ptr, stream_ptr
+    small = torch.empty(((k + n) * 8,), dtype=torch.uint8, device="cuda")
+    c3 = torch.empty((rows, n), dtype=torch.uint64, device="cuda")
+    check(LIB.vi_kquant_encode_rows(ptr(torch.from_numpy(raw).cuda()), int(qt[1]), float(S), d_out, d_in, int(transpose),
+                                    0, rows, ell, k, n, 1, ptr(seed_t), 5, None, ptr(c3), ptr(small), small.numel(),
+                                    stream_ptr()))
+    assert torch.equal(c3.view(torch.int64), want_c.view(torch.int64))
 
 
 # ---------------------------------------------------------------- sumcheck ---

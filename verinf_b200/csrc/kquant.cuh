@@ -99,6 +99,43 @@ __device__ __forceinline__ uint64_t lift_tab(const uint8_t* __restrict__ p, cons
     }
 }
 
+// ---- transposed staging ------------------------------------------------------------------------
+// For the transposed traversal (flat index f = k*d_out + n of the (d_in, d_out) view) consecutive
+// elements come from different super-blocks, so every element would cost two 32-byte sector
+// fetches for half a byte of payload.  A pre-pass therefore writes, in traversal order, one
+// byte per weight (the raw quant: 0..15 / 0..31 / 0..63) and the pre-multiplied sub-block
+// scales per (sub-block of k, n); the loader then reads 16 contiguous bytes and 16 contiguous
+// scales per tile row.  1.25 bytes per weight instead of the 8 of a lifted matrix.
+// Raw quant of element e of the super-block at p.
+template <int QT>
+__device__ __forceinline__ uint32_t raw_quant(const uint8_t* __restrict__ p, int e) {
+    if constexpr (QT == Q6_K) {
+        uint32_t lo = (__ldg(p + (e >> 7) * 64 + (e & 63)) >> (4 * ((e >> 6) & 1))) & 0xF;
+        uint32_t hi = (__ldg(p + 128 + (e >> 7) * 32 + (e & 31)) >> (2 * ((e >> 5) & 3))) & 3;
+        return lo | (hi << 4);
+    } else {
+        const uint8_t* qs = p + (QT == Q4_K ? 16 : 48);
+        uint32_t q = (__ldg(qs + (e >> 6) * 32 + (e & 31)) >> (4 * ((e >> 5) & 1))) & 0xF;
+        if constexpr (QT == Q5_K) q |= ((__ldg(p + 16 + (e & 31)) >> (e >> 5)) & 1) << 4;
+        return q;
+    }
+}
+// scales per sub-block of k in the staged layout: Q4_K/Q5_K float2 per 32 k, Q6_K float per 16 k
+__host__ __device__ constexpr int staged_sub_shift(int qtype) { return qtype == Q6_K ? 4 : 5; }
+__host__ __device__ constexpr int staged_scale_bytes(int qtype) { return qtype == Q6_K ? 4 : 8; }
+
+// element (k, n) from the staged arrays; same separately rounded fp32 operations as lift<>()
+__device__ __forceinline__ uint64_t lift_staged(int qtype, const uint8_t* __restrict__ qT, const void* __restrict__ sT,
+                                                uint32_t f, uint32_t k, uint32_t n, uint32_t d_out, double S) {
+    const uint32_t q = __ldg(qT + f);
+    if (qtype == Q6_K) {
+        const float sc = __ldg(reinterpret_cast<const float*>(sT) + (size_t)(k >> 4) * d_out + n);
+        return to_field(__fmul_rn(sc, (float)((int)q - 32)), S);
+    }
+    const float2 sm = __ldg(reinterpret_cast<const float2*>(sT) + (size_t)(k >> 5) * d_out + n);
+    return to_field(__fsub_rn(__fmul_rn(sm.x, (float)q), sm.y), S);
+}
+
 __device__ __forceinline__ uint64_t lift_any_tab(int qtype, const uint8_t* __restrict__ raw,
                                                  const float* __restrict__ table, int64_t widx, double S) {
     const int64_t b = widx >> 8;

@@ -153,6 +153,10 @@ struct PassArgs {
     double kq_S;
     int64_t kq_dout, kq_din, kq_first_row;
     const float* kq_table;   // pre-multiplied sub-block scales (vkq::fill_table) or null
+    const uint8_t* kq_qT;    // transposed staging (vkq::lift_staged): one byte per weight in traversal order,
+    const void* kq_sT;       //   and the scales per (sub-block of k, n); null = decode from the super-blocks
+    uint64_t kq_magic;       // floor(2^64 / kq_dout) + 1 when the matrix has fewer than 2^32 elements (then
+                             // f / kq_dout = umul64hi(f, kq_magic) exactly), else 0: 64-bit division
 };
 
 // Minimum resident CTAs per SM asked of the compiler for the 256-thread tiles (register budget =
@@ -208,9 +212,26 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
                         else {
                             int64_t f = (a.kq_first_row + item) * a.ell + slot;
                             if (f < a.kq_dout * a.kq_din) {
-                                int64_t widx = a.kq_transpose ? (f % a.kq_dout) * a.kq_din + f / a.kq_dout : f;
-                                x = a.kq_table ? vkq::lift_any_tab(a.kq_type, a.kq_raw, a.kq_table, widx, a.kq_S)
-                                               : vkq::lift_any(a.kq_type, a.kq_raw, widx, a.kq_S);
+                                if (a.kq_qT) {            // staged transposed layout: f = k*d_out + n
+                                    const uint32_t f32 = (uint32_t)f;
+                                    const uint32_t kk = (uint32_t)__umul64hi((uint64_t)f32, a.kq_magic);
+                                    x = vkq::lift_staged(a.kq_type, a.kq_qT, a.kq_sT, f32, kk,
+                                                         f32 - kk * (uint32_t)a.kq_dout, (uint32_t)a.kq_dout, a.kq_S);
+                                } else {
+                                    int64_t widx = f;
+                                    if (a.kq_transpose) {
+                                        if (a.kq_magic) {
+                                            const uint32_t f32 = (uint32_t)f;
+                                            const uint32_t q = (uint32_t)__umul64hi((uint64_t)f32, a.kq_magic);
+                                            const uint32_t r = f32 - q * (uint32_t)a.kq_dout;
+                                            widx = (int64_t)((uint64_t)r * (uint64_t)a.kq_din + q);
+                                        } else {
+                                            widx = (f % a.kq_dout) * a.kq_din + f / a.kq_dout;
+                                        }
+                                    }
+                                    x = a.kq_table ? vkq::lift_any_tab(a.kq_type, a.kq_raw, a.kq_table, widx, a.kq_S)
+                                                   : vkq::lift_any(a.kq_type, a.kq_raw, widx, a.kq_S);
+                                }
                             }
                         }
                     } else if (a.pad_mode == 1) x = vb3::pad_prg(seed, (uint64_t)(a.row_off + item), (uint64_t)(slot - a.ell));
@@ -254,6 +275,40 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
         for (int e = tid; e < L * C; e += nthr) {
             int k = e & (L - 1), cl = e >> LOGL;
             if (cl < ncols_tile) dst[(uint32_t)cl * a.out_col + (uint32_t)k * a.out_k] = sm[k * CP + cl];
+        }
+    }
+}
+
+// Transposed staging pre-pass: CTA = 32 output rows n x one super-block column (256 values of k).
+// Quants go through a shared-memory transpose so that both the reads (a super-block's bytes)
+// and the writes (32 consecutive n for one k) are contiguous.
+template <int QT>
+__global__ void __launch_bounds__(256) k_kq_stage_T(const uint8_t* __restrict__ raw, int64_t d_out, int64_t d_in,
+                                                    uint8_t* __restrict__ qT, void* __restrict__ sT) {
+    __shared__ uint8_t tile[256][33];
+    const int tid = threadIdx.x;
+    const int64_t n0 = (int64_t)blockIdx.x * 32, kb = blockIdx.y, bpr = d_in >> 8;   // super-blocks per matrix row
+    for (int nl = 0; nl < 32; ++nl) {
+        const int64_t n = n0 + nl;
+        if (n < d_out) tile[tid][nl] = (uint8_t)vkq::raw_quant<QT>(raw + (n * bpr + kb) * vkq::block_bytes(QT), tid);
+    }
+    __syncthreads();
+    const int nl = tid & 31;
+    if (n0 + nl < d_out) {
+#pragma unroll 4
+        for (int i = 0; i < 32; ++i) {
+            const int kk = (tid >> 5) + 8 * i;
+            qT[(kb * 256 + kk) * d_out + n0 + nl] = tile[kk][nl];
+        }
+        const uint8_t* p = raw + ((n0 + nl) * bpr + kb) * vkq::block_bytes(QT);
+        constexpr int SUBS = QT == vkq::Q6_K ? 16 : 8;
+        for (int sub = tid >> 5; sub < SUBS; sub += 8) {
+            float t[16];
+            vkq::fill_table<QT>(p, sub, t);
+            if constexpr (QT == vkq::Q6_K)
+                reinterpret_cast<float*>(sT)[(kb * 16 + sub) * d_out + n0 + nl] = t[sub];
+            else
+                reinterpret_cast<float2*>(sT)[(kb * 8 + sub) * d_out + n0 + nl] = make_float2(t[2 * sub], t[2 * sub + 1]);
         }
     }
 }
@@ -654,7 +709,8 @@ extern "C" int64_t vi_encode_scratch_bytes(int64_t m, int64_t k, int64_t n) {
 }
 
 namespace {
-struct KqSrc { const uint8_t* raw; int qtype; int transpose; double S; int64_t d_out, d_in, first_row; const float* table; };
+struct KqSrc { const uint8_t* raw; int qtype; int transpose; double S; int64_t d_out, d_in, first_row; const float* table;
+               const uint8_t* qT; const void* sT; };
 }
 
 static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t ell, int64_t k, int64_t n,
@@ -702,6 +758,9 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
             a.kq_raw = kq->raw; a.kq_type = kq->qtype; a.kq_transpose = kq->transpose; a.kq_S = kq->S;
             a.kq_dout = kq->d_out; a.kq_din = kq->d_in; a.kq_first_row = kq->first_row + r0;
             a.kq_table = kq->table;
+            a.kq_qT = kq->qT; a.kq_sT = kq->sT;
+            a.kq_magic = (kq->d_out >= 2 && kq->d_out * kq->d_in < (int64_t(1) << 32))
+                             ? ~uint64_t(0) / (uint64_t)kq->d_out + 1 : 0;
         } a.pad_mode = (ell < k) ? pad_mode : 0; a.row_off = row_off + r0;
         a.seed = seed_dev32;
         rc = launch_pass(log1, true, 0, a, cnt, st, vi::PROF_ENC_PASS1);
@@ -748,13 +807,32 @@ extern "C" int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, in
     VI_REQUIRE(qtype == 4 || qtype == 5 || qtype == 6, "kquant encode: qtype must be 4, 5 or 6");
     VI_REQUIRE(d_out > 0 && d_in > 0 && (d_out * d_in) % 256 == 0, "kquant encode: d_out*d_in must be a multiple of 256");
     VI_REQUIRE(first_row >= 0 && raw != nullptr, "kquant encode: bad source");
-    KqSrc kq{raw, qtype, transpose != 0, S, d_out, d_in, first_row, nullptr};
+    KqSrc kq{raw, qtype, transpose != 0, S, d_out, d_in, first_row, nullptr, nullptr, nullptr};
     // When the scratch has room beyond one row chunk, its tail holds the pre-multiplied sub-block
     // scales of the whole matrix (64 bytes per super-block), rebuilt on every call.
     const int64_t n_blocks = d_out * d_in / 256;
     const int64_t table_bytes = n_blocks * vkq::TABLE_BYTES_PER_BLOCK;
     const int64_t per_row = (k + (codes ? n : 0)) * 8;
-    if (m > 0 && scratch != nullptr && scratch_bytes >= per_row + table_bytes + 64) {
+    // Transposed traversal of a matrix whose rows are whole super-blocks: stage the quants and the
+    // scales in traversal order (1.25 bytes per weight at the scratch tail) when there is room.
+    const int64_t n_w = d_out * d_in;
+    const int64_t scale_bytes = (n_w >> vkq::staged_sub_shift(qtype)) * vkq::staged_scale_bytes(qtype);
+    const int64_t staged_bytes = ((n_w + 63) & ~int64_t(63)) + scale_bytes;
+    if (m > 0 && transpose && d_in % 256 == 0 && d_out >= 2 && n_w < (int64_t(1) << 32) && d_in / 256 <= 65535 &&
+        scratch != nullptr && scratch_bytes >= per_row + staged_bytes + 64) {
+        char* base = (char*)scratch + ((scratch_bytes - staged_bytes) & ~int64_t(63));
+        uint8_t* qT = (uint8_t*)base;
+        void* sT = base + ((n_w + 63) & ~int64_t(63));
+        dim3 grid((unsigned)((d_out + 31) / 32), (unsigned)(d_in / 256));
+        cudaStream_t st = (cudaStream_t)stream;
+        if (qtype == 4) k_kq_stage_T<vkq::Q4_K><<<grid, 256, 0, st>>>(raw, d_out, d_in, qT, sT);
+        else if (qtype == 5) k_kq_stage_T<vkq::Q5_K><<<grid, 256, 0, st>>>(raw, d_out, d_in, qT, sT);
+        else k_kq_stage_T<vkq::Q6_K><<<grid, 256, 0, st>>>(raw, d_out, d_in, qT, sT);
+        int rc = vi::check_launch("k_kq_stage_T");
+        if (rc) return rc;
+        kq.qT = qT; kq.sT = sT;
+        scratch_bytes = base - (char*)scratch;
+    } else if (m > 0 && scratch != nullptr && scratch_bytes >= per_row + table_bytes + 64) {
         char* tab = (char*)scratch + ((scratch_bytes - table_bytes) & ~int64_t(63));
         const int per = qtype == 6 ? 16 : 8;
         const int64_t threads = n_blocks * per;

@@ -57,7 +57,8 @@ def kquant_encode_rows(raw_u8_cuda, qtype, S, d_out, d_in, *, ell, k_deg, n_lig,
     codes = torch.empty((n_rows, n_lig), dtype=torch.uint64, device=dev) if need_codewords else None
     seed = master_seed.contiguous() if master_seed is not None else None
     with torch.cuda.device(dev):
-        nb = LIB.vi_encode_scratch_bytes(n_rows, k_deg, n_lig) + d_out * d_in // 4 + 128   # + scale table
+        # + the staging area of the loader: 1.25 bytes per weight (transposed) or 64 bytes per super-block
+        nb = LIB.vi_encode_scratch_bytes(n_rows, k_deg, n_lig) + (d_out * d_in * 5) // 4 + 256
         s = scratch(nb, dev) if nb else None
         check(LIB.vi_kquant_encode_rows(ptr(raw), _QTYPE[qtype], float(S), d_out, d_in, int(bool(transpose)),
                                         first_row, n_rows, ell, k_deg, n_lig, 1 if seed is not None else 0,

@@ -78,16 +78,15 @@ def kquant_fused_encode(dev, qtype="Q4_K", seed=3):
         return kq.kquant_encode_rows(raw_t, qtype, S, d_out, d_in, ell=ELL, k_deg=K_DEG, n_lig=N_LIG,
                                      transpose=True, master_seed=seed_t)[1]
 
-    a, _ = _timed(unfused)
-    b, _ = _timed(fused)
+    a, b = unfused(), fused()
     same = bool(torch.equal(a.view(torch.int64), b.view(torch.int64)))
-    del a
-    _, t_unf = _timed(unfused)
-    _, t_fus = _timed(fused)
     rows = b.size(0)
-    return {"qtype": qtype, "rows": rows, "bit_identical_to_unfused": same, "fused_ms": t_fus * 1e3,
-            "unfused_ms": t_unf * 1e3, "encoded_elems_per_s": rows * N_LIG / t_fus,
-            "codeword_gbs": rows * N_LIG * 8 / t_fus / 1e9}
+    del a, b
+    t_unf = _event_ms(unfused, reps=3, warm=1)
+    t_fus = _event_ms(fused, reps=3, warm=1)
+    return {"qtype": qtype, "rows": rows, "bit_identical_to_unfused": same, "fused_ms": t_fus,
+            "unfused_ms": t_unf, "encoded_elems_per_s": rows * N_LIG / t_fus * 1e3,
+            "codeword_gbs": rows * N_LIG * 8 / t_fus / 1e6}
 
 
 def _event_ms(fn, reps=5, warm=2):
