@@ -78,9 +78,14 @@ __device__ __forceinline__ uint64_t tw_at(const uint64_t* __restrict__ tw, uint3
 
 // Stages S..NS-1 of the tile DFT.  v is preloaded for stage S; on return it holds
 // the outputs of the last stage (see Sched::last_k).  sm is the tile [pos*CP + col].
-template <int LOGL, bool INV, bool SMALL_LAST, int S>
+// RHO0 > 0 (forward only): the transform is the coset t of a length RHO0*L transform, input
+// pre-multiplied by w_{RHO0*L}^(t*l) except for the factor common to a thread's first butterfly,
+// w_{RHO0*L}^(t*qp), which is folded into the stage-0 twiddle here: w_L^(qp*c) * w_{RHO0*L}^(t*qp)
+// = tw0[qp*(RHO0*c + t)] with tw0 the table of w_{RHO0*L}.
+template <int LOGL, bool INV, bool SMALL_LAST, int S, int RHO0 = 0>
 __device__ __forceinline__ void run_stages(uint64_t (&v)[Sched<LOGL, SMALL_LAST>::EPT], uint64_t* sm,
-                                           int CP, int col, int w, const uint64_t* __restrict__ twL) {
+                                           int CP, int col, int w, const uint64_t* __restrict__ twL,
+                                           const uint64_t* __restrict__ tw0 = nullptr, int t = 0) {
     using SC = Sched<LOGL, SMALL_LAST>;
     if constexpr (S < SC::NS) {
         constexpr int LOGR = SC::logr(S), R = 1 << LOGR, G = SC::EPT / R, LOGP = SC::logp(S);
@@ -99,10 +104,17 @@ __device__ __forceinline__ void run_stages(uint64_t (&v)[Sched<LOGL, SMALL_LAST>
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 uint32_t qp = (uint32_t)(w + g * SC::TPC) >> LOGP;
+                if constexpr (S == 0 && RHO0 > 0) {
+                    static_assert(!INV && LOGP == 0, "coset twiddles: forward stage 0 only");
 #pragma unroll
-                for (int c = 1; c < R; ++c) {
-                    uint32_t e = (qp * c) << LOGP;
-                    v[g * R + brev(c, LOGR)] = mul(v[g * R + brev(c, LOGR)], tw_at<INV>(twL, e, L - 1));
+                    for (int c = 0; c < R; ++c)
+                        v[g * R + brev(c, LOGR)] = mul(v[g * R + brev(c, LOGR)], __ldg(tw0 + qp * (uint32_t)(RHO0 * c + t)));
+                } else {
+#pragma unroll
+                    for (int c = 1; c < R; ++c) {
+                        uint32_t e = (qp * c) << LOGP;
+                        v[g * R + brev(c, LOGR)] = mul(v[g * R + brev(c, LOGR)], tw_at<INV>(twL, e, L - 1));
+                    }
                 }
             }
             __syncthreads();
@@ -115,7 +127,7 @@ __device__ __forceinline__ void run_stages(uint64_t (&v)[Sched<LOGL, SMALL_LAST>
                     sm[(qp * PP * R + kappa + PP * c) * CP + col] = v[g * R + brev(c, LOGR)];
             }
             __syncthreads();
-            run_stages<LOGL, INV, SMALL_LAST, S + 1>(v, sm, CP, col, w, twL);
+            run_stages<LOGL, INV, SMALL_LAST, S + 1, RHO0>(v, sm, CP, col, w, twL, tw0, t);
         }
     }
 }
@@ -346,14 +358,42 @@ struct MidArgs {
     const uint64_t* fsK;   // forward four-step factors, fsK[m1*n1 + l2] = w_K^(l2*m1)
     const uint64_t* twist; // (rho, K): (7*w_N^t)^l
     uint64_t k_inv;
+    // shift-twist form (RHO template parameter 2 or 4):
+    const uint64_t* cscale;  // K entries: K^-1 * 7^l
+    const uint64_t* twRL;    // w_{rho*L}^e, e < rho*L (stage-0 twiddles of the coset transforms)
+    const uint64_t* fsN;     // N entries: fsN[kk*n1 + l2] = w_N^(l2*kk), kk = rho*m1 + t
 };
 
-template <int LOGL>
+// x * 2^E mod p for a compile-time E in [0, 192) (2^96 = -1)
+template <int E>
+__device__ __forceinline__ uint64_t mul_pow2_any(uint64_t x) {
+    if constexpr (E == 0) return x;
+    else if constexpr (E < 96) return vgl::mul_pow2<E>(x);
+    else return vgl::sub(0, vgl::mul_pow2<E - 96>(x));
+}
+// v[j] = c[j] * w_{16*RHO}^(T*j), j < 16: the part of the coset twist that varies inside a thread's
+// first radix-16 butterfly; w_{16*RHO} is a power of two for RHO <= 4, so these are shifts.
+template <int RHO, int T, int J = 0>
+__device__ __forceinline__ void coset_shift(const uint64_t (&c)[16], uint64_t (&v)[16]) {
+    if constexpr (J < 16) {
+        constexpr int E = (vdft::root_exp(RHO == 4 ? 6 : RHO == 2 ? 5 : 4) * T * J) % 192;
+        v[J] = mul_pow2_any<E>(c[J]);
+        coset_shift<RHO, T, J + 1>(c, v);
+    }
+}
+
+// RHO = 0: any blow-up factor, twist read from the (rho, K) table (one full multiply per element
+// and coset).  RHO = 2 or 4 (tile length >= 16): the twist (7 w_N^t)^l with l = l1*n1 + l2,
+// l1 = w + j*(L/16), is split into  K^-1 7^l (folded into the coefficient scaling, once),
+// w_N^(t*l2) (folded into the four-step factor table), w_{RHO L}^(t*w) (folded into the stage-0
+// twiddle) and w_{16 RHO}^(t*j), a power of two applied as a shift: no twist multiply remains.
+template <int LOGL, int RHO>
 __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? VI_MID_MINB : 1) k_encode_mid(MidArgs a) {
     using SI = Sched<LOGL, false>;   // inverse: small stage first, radix-16 last
     using SF = Sched<LOGL, true>;    // forward: radix-16 first, small stage last
     constexpr int L = 1 << LOGL, EPT = SI::EPT;
     constexpr int LR = SI::NS ? SI::logr(SI::NS - 1) : 0;   // last inverse radix == first forward radix
+    static_assert(RHO == 0 || (LOGL >= 4 && (RHO == 2 || RHO == 4)), "shift-twist form needs radix-16 first stages");
     extern __shared__ uint64_t sm[];
     const int tid = threadIdx.x, C = 1 << a.logC, CP = C + 1;
     const int col = tid & (C - 1), w = tid >> a.logC;
@@ -377,32 +417,65 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
 #pragma unroll
     for (int j = 0; j < EPT; ++j) c[j] = sm[SI::first_pos(j, w) * CP + col];
     run_stages<LOGL, true, false, 0>(c, sm, CP, col, w, a.twL);
+    if constexpr (RHO == 0) {
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) c[j] = mul(c[j], a.k_inv);
+        for (int j = 0; j < EPT; ++j) c[j] = mul(c[j], a.k_inv);
+    }
     if (a.polys && valid) {
         uint64_t* dst = a.polys + item * a.K + colg;
 #pragma unroll
-        for (int j = 0; j < EPT; ++j) dst[(uint32_t)SI::last_k(j, w) * n1] = c[j];
+        for (int j = 0; j < EPT; ++j) dst[(uint32_t)SI::last_k(j, w) * n1] = RHO == 0 ? c[j] : mul(c[j], a.k_inv);
     }
     if (!a.s2) return;
     uint64_t* dst2 = a.s2 + item * a.K * a.rho + colg;
-    for (int t = 0; t < a.rho; ++t) {
-        const uint64_t* tw_t = a.twist + (int64_t)t * a.K + colg;
-        if (SF::NS > 1) __syncthreads();   // previous coset finished reading the tile
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            // forward register j needs coefficient index l1 = first_pos(j): it is held in c[brev(j)]
-            uint32_t l1 = SF::first_pos(j, w);
-            uint64_t tw = valid ? __ldg(tw_t + n1 * l1) : 0;
-            v[j] = mul(c[(j / (1 << LR)) * (1 << LR) + brev(j % (1 << LR), LR)], tw);
-        }
-        run_stages<LOGL, false, true, 0>(v, sm, CP, col, w, a.twL);
-        if (valid) {
+    if constexpr (RHO == 0) {
+        for (int t = 0; t < a.rho; ++t) {
+            const uint64_t* tw_t = a.twist + (int64_t)t * a.K + colg;
+            if (SF::NS > 1) __syncthreads();   // previous coset finished reading the tile
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
-                uint32_t m1 = SF::last_k(j, w);
-                uint64_t x = mul(v[j], __ldg(a.fsK + colg + m1 * n1));
-                dst2[(m1 * rho + (uint32_t)t) * n1] = x;
+                // forward register j needs coefficient index l1 = first_pos(j): it is held in c[brev(j)]
+                uint32_t l1 = SF::first_pos(j, w);
+                uint64_t tw = valid ? __ldg(tw_t + n1 * l1) : 0;
+                v[j] = mul(c[(j / (1 << LR)) * (1 << LR) + brev(j % (1 << LR), LR)], tw);
+            }
+            run_stages<LOGL, false, true, 0>(v, sm, CP, col, w, a.twL);
+            if (valid) {
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    uint32_t m1 = SF::last_k(j, w);
+                    uint64_t x = mul(v[j], __ldg(a.fsK + colg + m1 * n1));
+                    dst2[(m1 * rho + (uint32_t)t) * n1] = x;
+                }
+            }
+        }
+    } else {
+        // c2[j] = coefficient l1 = first_pos(j) (held in c[brev(j)]) times K^-1 7^l, l = l1*n1 + l2
+        uint64_t c2[EPT];
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            uint32_t l1 = SF::first_pos(j, w);
+            uint64_t sc = valid ? __ldg(a.cscale + colg + n1 * l1) : 0;
+            c2[j] = mul(c[brev(j, LR)], sc);
+        }
+#pragma unroll 1
+        for (int t = 0; t < RHO; ++t) {
+            if (SF::NS > 1) __syncthreads();   // previous coset finished reading the tile
+            switch (t) {
+                case 0: coset_shift<RHO, 0>(c2, v); break;
+                case 1: coset_shift<RHO, 1>(c2, v); break;
+                case 2: coset_shift<RHO, 2 % RHO>(c2, v); break;
+                default: coset_shift<RHO, 3 % RHO>(c2, v); break;
+            }
+            run_stages<LOGL, false, true, 0, RHO>(v, sm, CP, col, w, a.twL, a.twRL, t);
+            if (valid) {
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    uint32_t m1 = SF::last_k(j, w);
+                    uint32_t kk = m1 * RHO + (uint32_t)t;
+                    uint64_t x = mul(v[j], __ldg(a.fsN + colg + kk * n1));
+                    dst2[kk * n1] = x;
+                }
             }
         }
     }
@@ -414,6 +487,7 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
 struct DevTables {
     std::map<int64_t, uint64_t*> tw;                          // n -> w_n^e, e < n
     std::map<std::pair<int64_t, int64_t>, uint64_t*> twist;   // (K, N) -> (rho, K)
+    std::map<int64_t, uint64_t*> cscale;                      // K -> K^-1 * 7^l
     std::map<std::tuple<int64_t, int64_t, bool>, uint64_t*> fs;   // (n, ncols, inverse) -> four-step factors
 };
 std::mutex g_mu;
@@ -488,6 +562,25 @@ int get_twist(int64_t K, int64_t N, const uint64_t** out) {
     return VI_OK;
 }
 
+// K^-1 * 7^l, l < K: coefficient scaling of the shift-twist form of the encode
+int get_cscale(int64_t K, const uint64_t** out) {
+    int dev;
+    VI_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto& T = g_tables[dev];
+    auto it = T.cscale.find(K);
+    if (it != T.cscale.end()) { *out = it->second; return VI_OK; }
+    std::vector<uint64_t> h((size_t)K);
+    uint64_t cur = vgl::hpow(vgl::hpow(2, (uint64_t)vi::ilog2(K)), vgl::P - 2);     // K^-1
+    for (int64_t l = 0; l < K; ++l) { h[(size_t)l] = cur; cur = vgl::hmul(cur, 7); }
+    uint64_t* d = nullptr;
+    VI_CUDA(cudaMalloc(&d, (size_t)K * 8));
+    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)K * 8, cudaMemcpyHostToDevice));
+    T.cscale[K] = d;
+    *out = d;
+    return VI_OK;
+}
+
 constexpr int MAX_LOGL = 12;      // tile DFT length up to 4096 (2 columns per tile) -> two-pass transforms up to 2^24
 constexpr int SINGLE_LOGL = 10;   // transforms up to this length run as one pass over 16-row tiles
 
@@ -540,10 +633,10 @@ int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaSt
     return mode ? launch_pass_l<false, 1>(logL, a, items, st, tag) : launch_pass_l<false, 0>(logL, a, items, st, tag);
 }
 
-template <int LOGL>
+template <int LOGL, int RHO>
 int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
     size_t smem = tile_smem(LOGL, a.logC);
-    auto fn = k_encode_mid<LOGL>;
+    auto fn = k_encode_mid<LOGL, RHO>;
     if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = items * a.tiles_per_item;
     if (grid <= 0) return VI_OK;
@@ -552,9 +645,22 @@ int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
     fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
     return vi::check_launch("k_encode_mid");
 }
+// blow-up factors and tile lengths for which the shift-twist kernels are built
+// (VERINF_MID_SHIFT=0 selects the table-twist kernels everywhere, for comparison)
+bool mid_shift_form(int logL, int64_t rho) {
+    static const bool on = [] { const char* e = getenv("VERINF_MID_SHIFT"); return !(e && e[0] == '0'); }();
+    return on && (rho == 2 || rho == 4) && logL >= 4 && logL <= 10;
+}
 int launch_mid(int logL, const MidArgs& a, int64_t items, cudaStream_t st) {
+    if (mid_shift_form(logL, a.rho)) {
+        switch (logL * 8 + a.rho) {
+#define VI_CASE(x) case x * 8 + 2: return launch_mid_t<x, 2>(a, items, st); case x * 8 + 4: return launch_mid_t<x, 4>(a, items, st);
+            VI_CASE(4) VI_CASE(5) VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
+#undef VI_CASE
+        }
+    }
     switch (logL) {
-#define VI_CASE(x) case x: return launch_mid_t<x>(a, items, st);
+#define VI_CASE(x) case x: return launch_mid_t<x, 0>(a, items, st);
         VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
         VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10) VI_CASE(11) VI_CASE(12)
 #undef VI_CASE
@@ -739,8 +845,16 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
     const uint64_t *fs_inv, *fs_fwd = nullptr, *twist = nullptr;
     int rc = get_fs(k, n2, true, &fs_inv);        // inverse step 1: columns j2 (n2 of them), index k1
     if (rc) return rc;
-    if (codes) { rc = get_fs(k, n1, false, &fs_fwd); if (rc) return rc; }   // forward step 1: columns l2 (n1), index m1
-    if (codes) { rc = get_twist(k, n, &twist); if (rc) return rc; }
+    const uint64_t *cscale = nullptr, *twRL = nullptr, *fsN = nullptr;
+    const bool shift_form = codes && mid_shift_form(log2, rho);
+    if (shift_form) {
+        rc = get_cscale(k, &cscale); if (rc) return rc;
+        rc = get_tw(rho * n2, &twRL); if (rc) return rc;
+        rc = get_fs(n, n1, false, &fsN); if (rc) return rc;                  // w_N^(l2*(rho*m1 + t))
+    } else if (codes) {
+        rc = get_fs(k, n1, false, &fs_fwd); if (rc) return rc;               // forward step 1: columns l2 (n1), index m1
+        rc = get_twist(k, n, &twist); if (rc) return rc;
+    }
     uint64_t* s1 = (uint64_t*)scratch;
     for (int64_t r0 = 0; r0 < m; r0 += chunk) {
         int64_t cnt = m - r0 < chunk ? m - r0 : chunk;
@@ -771,6 +885,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         mid.logC = pick_logC(log2, n1);
         mid.n1 = n1; mid.tiles_per_item = (n1 + (1 << mid.logC) - 1) >> mid.logC;
         mid.rho = (int)rho; mid.K = k; mid.fsK = fs_fwd; mid.twist = twist; mid.k_inv = inv_pow2(logk);
+        mid.cscale = cscale; mid.twRL = twRL; mid.fsN = fsN;
         rc = get_tw(n2, &mid.twL);
         if (rc) return rc;
         rc = launch_mid(log2, mid, cnt, st);
