@@ -135,6 +135,31 @@ __device__ __forceinline__ uint64_t mul(uint64_t a, uint64_t b) {
     return reduce128(pack((uint32_t)t, (uint32_t)v), w);
 }
 
+// (x4:x3:x2:x1:x0) += a * b as integers: 8 multiply-adds with carry + 5 carry propagations,
+// no modular reduction.  x4 counts the carries out of 2^128, so 2^32 products fit.
+__device__ __forceinline__ void mac160(uint32_t (&x)[5], uint64_t a, uint64_t b) {
+    const uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
+    asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
+        "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
+        "madc.lo.cc.u32 %2, %6, %8, %2;\n\t"
+        "madc.hi.cc.u32 %3, %6, %8, %3;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %1, %5, %8, %1;\n\t"
+        "madc.hi.cc.u32 %2, %5, %8, %2;\n\t"
+        "addc.cc.u32 %3, %3, 0;\n\t"
+        "addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %1, %6, %7, %1;\n\t"
+        "madc.hi.cc.u32 %2, %6, %7, %2;\n\t"
+        "addc.cc.u32 %3, %3, 0;\n\t"
+        "addc.u32 %4, %4, 0;"
+        : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(b1));
+}
+// the 160-bit sum mod p: 2^128 = -2^32 (mod p), and x4 << 32 <= p - 1 is canonical
+__device__ __forceinline__ uint64_t reduce160(const uint32_t (&x)[5]) {
+    return sub(reduce128(pack(x[0], x[1]), pack(x[2], x[3])), (uint64_t)x[4] << 32);
+}
+
 __host__ __device__ __forceinline__ uint64_t neg(uint64_t a) { return a == 0 ? 0 : P - a; }
 
 __device__ __forceinline__ uint64_t pow(uint64_t base, uint64_t e) {
