@@ -265,8 +265,8 @@ def run_native(a):
         dom = max(prof.items(), key=lambda kv: kv[1][0])
         per_row = {"encode_pass1": 8 * (k + k), "encode_mid": 8 * (k + n), "encode_pass3": 8 * (n + n),
                    "hash_columns": 8 * n}
-        # DRAM bytes per message row from the committed ncu captures (profiles/*.md: dram read + write of
-        # one launch / rows of that launch), valid for this geometry only; scaled to an average launch
+        # DRAM bytes per message row from ncu captures of these kernels (dram read + write of one launch /
+        # rows of that launch), valid for this geometry only; scaled to an average launch
         ncu_per_row = {"encode_pass1": 1.597e6, "encode_mid": 2.515e6, "encode_pass3": 4.343e6,
                        "hash_columns": 2.197e6} if (a.log_k, a.blowup) == (16, 4) else {}
         launches = sum(v[1] for v in prof.values())
@@ -275,7 +275,7 @@ def run_native(a):
         achieved = bytes_per_step / (dom_ms_per_step * 1e-3) / 1e9 if dom_ms_per_step else 0.0
         enc_ms = sum(prof.get(t_, (0, 0))[0] for t_ in ("encode_pass1", "encode_mid", "encode_pass3")) / a.steps
         # integer roofline of the encode: radix-16 butterfly element-stages and full modular multiplies at
-        # their measured ALU-pipe cost (profiles/int_pipes_sm100a.md: 8.8 and 17.3 ALU lane-ops), against
+        # their ALU-pipe cost measured with the integer-pipe microbenchmark (8.8 and 17.3 ALU lane-ops), against
         # 148 SMs x 64 ALU lanes per clock at the SM clock sampled during the run
         log_n = a.log_k
         stages_per_row = (1 + a.blowup) * k * log_n

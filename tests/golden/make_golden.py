@@ -19,7 +19,9 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference").resolve()
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/reference [fixture ...]")
+REF = Path(sys.argv[1]).resolve()
 sys.path.insert(0, str(REF))
 sys.path.insert(0, str(REF / "prover" / "ref"))
 
@@ -92,7 +94,7 @@ def encode_vectors():
 
 
 def config1():
-    """BASELINE config 1: 64 rows x 2^10 uniform in [0,p) from seed 0, K=2^10, N=2^12,
+    """The reference's CPU-runnable commit case: 64 rows x 2^10 uniform in [0,p) from seed 0, K=2^10, N=2^12,
     column leaves + Merkle root.  The full codeword matrix is 2 MiB, so the fixture keeps
     its sha256, four full rows, 16 full columns, all leaves' sha256 and the root."""
     cfg = protocol.Config(ELL=1024, K_DEG=1024, N_LIG=4096, T_QUERIES=4)

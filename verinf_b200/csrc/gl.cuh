@@ -180,8 +180,8 @@ __device__ __forceinline__ uint64_t pow(uint64_t base, uint64_t e) {
 //   S <  64: the general 128-bit reduction of (l2:l1:l0:0)
 //   S >= 64: l0*(2^32-1) - (l2:l1)
 // (Issuing the limb shifts as wide multiplies on the FMA pipe, or building the 64-bit sums from
-// mad.wide plus a 64-bit compare instead of carry chains, was measured slower on B200: see
-// profiles/int_pipes_sm100a.md.)
+// mad.wide plus a 64-bit compare instead of carry chains, was measured slower on B200: radix-16
+// butterfly throughput 2004 and 1250 G element-stages/s against 2091 for this form.)
 template <int S>
 __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
     static_assert(S >= 0 && S < 96, "shift out of range");

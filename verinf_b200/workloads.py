@@ -54,7 +54,7 @@ def _timed(fn):
 
 
 def kquant_fused_encode(dev, qtype="Q4_K", seed=3):
-    """BASELINE config 3: 11008x4096 weight as K-quant super-blocks -> lifted and RS-encoded
+    """Fused lift + encode workload: 11008x4096 weight as K-quant super-blocks -> lifted and RS-encoded
     (transposed view, 5504 rows).  Compares the fused op with lift + transpose + pack + encode."""
     d_out, d_in = 11008, 4096
     nb = d_out * d_in // 256
@@ -140,7 +140,7 @@ def fold_products(dev, rows=1024, k_deg=K_DEG, seed=9):
 
 
 def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
-    """BASELINE config 5 (dense variant): int8 weights/activations of one Llama-2-7B-shaped layer,
+    """Full-layer workload (dense row packing): int8 weights/activations of one Llama-2-7B-shaped layer,
     every weight and activation tensor committed (encode + column hash + Merkle), one deg-2
     sumcheck per matmul on the projected vectors.  Returns stage seconds."""
     g = torch.Generator(device=dev)
