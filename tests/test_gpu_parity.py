@@ -763,3 +763,23 @@ def test_fold_indexed_rows_and_edges(cp):
         fold.product_colsum(EA, EB, None, torch.tensor([rows], device="cuda"), torch.tensor([0], device="cuda"))
     with pytest.raises(RuntimeError):
         fold.ntt_forward_padded(dev(A), 128)                # rows longer than the transform
+
+
+@pytest.mark.parametrize("rows,slices", [(600, 16), (2100, 16), (4096, 16), (1024, 3), (129, 1), (100, 4)])
+def test_commit_host_equals_device_commit(cp, rows, slices):
+    """pinned-host commit (sliced copies overlapped with the encode, column hash streamed per slice)
+    gives the root of the one-shot device commit"""
+    from verinf_b200 import commit
+    rng = np.random.default_rng(rows)
+    ell, k, n = 48, 64, 256
+    msg = rnd_field(rng, (rows, ell))
+    seed_t = torch.arange(32, dtype=torch.uint8, device="cuda")
+    com = commit.RowCommitter(rows, ell, k, n, master_seed=seed_t, h2d_slices=slices)
+    want = com.commit(dev(msg), row_offset=9).cpu().numpy().tobytes()
+    pinned = torch.from_numpy(msg.view(np.int64)).view(torch.uint64).pin_memory()
+    assert com.commit_host(pinned, row_offset=9) == want
+    assert com.commit_host(pinned, row_offset=9) == want          # buffers are reused
+    padded = np.zeros((rows, k), dtype=np.uint64)
+    padded[:, :ell] = msg
+    padded[:, ell:] = oracle.row_prg(bytes(range(32)), 9, rows, k - ell)
+    assert oracle.commit_rows(padded, n) == want

@@ -73,7 +73,7 @@ class RowCommitter:
                       the root as 32 bytes on the host.
     """
 
-    def __init__(self, rows, ell, k_deg, n_lig, *, master_seed=None, device="cuda", h2d_slices=8):
+    def __init__(self, rows, ell, k_deg, n_lig, *, master_seed=None, device="cuda", h2d_slices=16):
         self.rows, self.ell, self.k, self.n = int(rows), int(ell), int(k_deg), int(n_lig)
         self.device = torch.device(device)
         self.seed = master_seed
@@ -88,6 +88,7 @@ class RowCommitter:
         self._stage = None
         self._copy_stream = None
         self._slices = max(1, int(h2d_slices))
+        self._stream_state = None
         self._root_host = torch.empty(32, dtype=torch.uint8).pin_memory() if dev.type == "cuda" else None
 
     @property
@@ -122,6 +123,14 @@ class RowCommitter:
                 self._copy_stream = torch.cuda.Stream(device=self.device)
             main = torch.cuda.current_stream()
             step = (self.rows + self._slices - 1) // self._slices
+            # slices of whole 128-row BLAKE3 chunks are hashed as soon as they are encoded (streaming
+            # column hash), so that after the last copy only one slice of work remains
+            streamed = self.rows > 128 and step >= 128
+            if streamed:
+                step = (step // 128) * 128
+                if self._stream_state is None:
+                    nb = LIB.vi_hash_stream_state_bytes(self.n, self.rows)
+                    self._stream_state = torch.empty(max(nb, 256), dtype=torch.uint8, device=self.device)
             self._copy_stream.wait_stream(main)       # previous commit no longer reads the staging buffer
             events = []
             with torch.cuda.stream(self._copy_stream):
@@ -134,7 +143,14 @@ class RowCommitter:
             for r0, cnt, ev in events:
                 main.wait_event(ev)
                 self._encode(self._stage[r0:r0 + cnt].data_ptr(), r0, cnt, row_offset)
-            self._hash_and_tree()
+                if streamed:
+                    check(LIB.vi_hash_stream_update(ptr(self._stream_state), self.n, self.rows, r0,
+                                                    self.codes[r0:r0 + cnt].data_ptr(), cnt, ptr(self.leaves),
+                                                    stream_ptr()))
+            if streamed:
+                check(LIB.vi_merkle_build(ptr(self.leaves), self.n, ptr(self.upper), stream_ptr()))
+            else:
+                self._hash_and_tree()
             self._root_host.copy_(self.root, non_blocking=True)
             main.synchronize()
         return bytes(self._root_host.tolist())
