@@ -233,6 +233,13 @@ int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t si
 int vi_poly_eval(const uint64_t* coeffs, int64_t m, int64_t d, const uint64_t* points, int64_t k,
                  uint64_t* out, void* stream);
 int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n, void* stream);
+/* The same product on the integer tensor cores (no counterpart in the reference): operands are
+ * split into byte planes in the scratch (vi_gl_matmul_tc_scratch_bytes(m, k, n) = 8 bytes per
+ * padded operand element, 16-byte aligned), the 64 plane products run as u8 x u8 -> s32
+ * mma.sync tiles and are recombined mod p.  Bit-identical to vi_gl_matmul. */
+int64_t vi_gl_matmul_tc_scratch_bytes(int64_t m, int64_t k, int64_t n);
+int vi_gl_matmul_tc(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n,
+                    void* scratch, int64_t scratch_bytes, void* stream);
 int vi_gl_matvec(const uint64_t* M, const uint64_t* v, uint64_t* w, int64_t m, int64_t n, void* stream);
 int vi_gl_spmv(const uint64_t* values, const uint64_t* col_idx, const uint64_t* row_ptr,
                const uint64_t* x, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,

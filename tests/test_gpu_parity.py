@@ -480,14 +480,14 @@ def test_linear_algebra(cp):
     # tile edges, the unaligned loader (odd n / odd k), more than one reduction period (k > 1024)
     for (m_, k_, n_) in ((64, 32, 32), (70, 2100, 45), (130, 1025, 64), (3, 1, 2), (64, 4096, 96), (33, 999, 34)):
         A2, B2 = rnd_field(rng, (m_, k_)), rnd_field(rng, (k_, n_))
-        assert np.array_equal(host(cp.gl_matmul(dev(A2), dev(B2))), oracle.gl_matmul(A2, B2)), (m_, k_, n_)
+        assert np.array_equal(host(cp.gl_matmul(dev(A2), dev(B2), force_simt=True)), oracle.gl_matmul(A2, B2)), (m_, k_, n_)
     # largest operands: every limb product and every accumulator at its bound
     A3 = np.full((64, 3072), P - 1, dtype=np.uint64)
     B3 = np.full((3072, 32), P - 1, dtype=np.uint64)
-    assert np.array_equal(host(cp.gl_matmul(dev(A3), dev(B3))), oracle.gl_matmul(A3, B3))
+    assert np.array_equal(host(cp.gl_matmul(dev(A3), dev(B3), force_simt=True)), oracle.gl_matmul(A3, B3))
     A3[:] = np.uint64(0xFFFFFFFEFFFFFFFF)      # below p, both 32-bit limbs of a near their maximum
     B3[:] = np.uint64(0xFFFFEFFFFFFFFFFF)      # below p, the two 22-bit limbs of b all ones
-    assert np.array_equal(host(cp.gl_matmul(dev(A3), dev(B3))), oracle.gl_matmul(A3, B3))
+    assert np.array_equal(host(cp.gl_matmul(dev(A3), dev(B3), force_simt=True)), oracle.gl_matmul(A3, B3))
     z = cp.gl_matmul(dev(A2[:, :0]), dev(B2[:0]))
     assert tuple(z.shape) == (33, 34) and not host(z).any()
     v = rnd_field(rng, 65)
@@ -608,6 +608,42 @@ def test_more_rows_than_a_grid_dimension(cp):
     assert np.array_equal(host(codes)[idx], oracle.encode_rows(padded, 32, want_polys=False)[1])
     leaves = cp.hash_columns_streamed(codes)
     assert np.array_equal(leaves.cpu().numpy(), oracle.hash_columns(host(codes)))
+
+
+def _matmul_tc(A, B):
+    from verinf_b200._lib import LIB, check, ptr, stream_ptr
+    m, k = A.shape
+    n = B.shape[1]
+    nb = LIB.vi_gl_matmul_tc_scratch_bytes(m, k, n)
+    sc = torch.empty(max(nb, 16), dtype=torch.uint8, device="cuda")
+    out = torch.empty((m, n), dtype=torch.uint64, device="cuda")
+    a_d, b_d = dev(A), dev(B)
+    check(LIB.vi_gl_matmul_tc(ptr(a_d), ptr(b_d), ptr(out), m, k, n, ptr(sc), nb, stream_ptr()))
+    return host(out)
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 32, 32), (1, 1, 1), (3, 5, 2), (70, 2100, 45), (130, 4096, 64), (65, 4097, 33),
+                                   (16, 9000, 40), (200, 300, 500)])
+def test_matmul_tensor_cores_vs_oracle(cp, m, k, n):
+    """byte-plane product on the integer tensor cores: ragged tiles, several 4096-term chunks"""
+    rng = np.random.default_rng(m * 7 + k + n)
+    A, B = rnd_field(rng, (m, k)), rnd_field(rng, (k, n))
+    assert np.array_equal(_matmul_tc(A, B), oracle.gl_matmul(A, B))
+
+
+def test_matmul_tensor_cores_extreme_operands(cp):
+    # every byte 0xff where the field allows it: all 15 plane sums reach their bound within a chunk
+    A = np.full((64, 8192), 0xFFFFFFFEFFFFFFFF, dtype=np.uint64)
+    B = np.full((8192, 32), 0xFFFFFFFEFFFFFFFF, dtype=np.uint64)
+    assert np.array_equal(_matmul_tc(A, B), oracle.gl_matmul(A, B))
+    A[:] = np.uint64(P - 1)
+    assert np.array_equal(_matmul_tc(A, B), oracle.gl_matmul(A, B))
+    # the Python entry point takes the tensor-core path for large products and the scalar one otherwise
+    rng = np.random.default_rng(1)
+    A, B = rnd_field(rng, (256, 512)), rnd_field(rng, (512, 128))
+    got = cp.gl_matmul(dev(A), dev(B))
+    assert np.array_equal(host(got), oracle.gl_matmul(A, B))
+    assert torch.equal(got.view(torch.int64), cp.gl_matmul(dev(A), dev(B), force_simt=True).view(torch.int64))
 
 
 # ---------------------------------------------------------------- openings ----

@@ -262,15 +262,25 @@ def poly_mul_batched(A, B):
 
 
 # ---- linear algebra mod P ----------------------------------------------------------------
-def gl_matmul(A, B):
+_TC_MIN_MACS = 1 << 22      # below this the plane split costs more than it saves
+
+
+def gl_matmul(A, B, force_simt=False):
     _chk_u64(A, "A"); _chk_u64(B, "B")
     if A.dim() != 2 or B.dim() != 2:
         raise RuntimeError("gl_matmul: 2-D inputs")
     if A.size(1) != B.size(0):
         raise RuntimeError("gl_matmul: inner dim mismatch")
-    Cm = torch.empty((A.size(0), B.size(1)), dtype=_U64, device=A.device)
+    m, k, n = A.size(0), A.size(1), B.size(1)
+    Cm = torch.empty((m, n), dtype=_U64, device=A.device)
     with torch.cuda.device(A.device):
-        check(LIB.vi_gl_matmul(ptr(A), ptr(B), ptr(Cm), A.size(0), A.size(1), B.size(1), stream_ptr()))
+        if m * k * n >= _TC_MIN_MACS and not force_simt:
+            # large products: byte planes on the integer tensor cores (same result)
+            nb = LIB.vi_gl_matmul_tc_scratch_bytes(m, k, n)
+            sc = scratch(nb, A.device, "matmul")
+            check(LIB.vi_gl_matmul_tc(ptr(A), ptr(B), ptr(Cm), m, k, n, ptr(sc), nb, stream_ptr()))
+        else:
+            check(LIB.vi_gl_matmul(ptr(A), ptr(B), ptr(Cm), m, k, n, stream_ptr()))
     return Cm
 
 
