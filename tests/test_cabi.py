@@ -87,7 +87,7 @@ def test_argument_validation_without_gpu(lib):
     assert L.vi_gl_matmul_tc(p, p, p, 4, 4, 4, None, 0, None) != 0 and "alias" in _err(lib)
     buf2 = (C.c_uint64 * 64)()
     assert L.vi_gl_matmul_tc(p, p, C.cast(buf2, C.c_void_p), 4, 4, 4, None, 0, None) != 0 and "scratch" in _err(lib)
-    assert L.vi_gl_matmul_tc_scratch_bytes(1, 1, 1) == 8 * (64 + 32) * 32
+    assert L.vi_gl_matmul_tc_scratch_bytes(1, 1, 1) == 8 * (64 + 32) * 64
     assert L.vi_gl_matmul_tc_scratch_bytes(1000, 4096, 11008) == 8 * (1024 + 11008) * 4096
     assert L.vi_gl_matmul_tc(p, p, p, 0, 4, 4, None, 0, None) == 0
     assert L.vi_open_columns(p, 4, 8, p, 2, p, 3, 0, None) != 0 and "stride" in _err(lib)

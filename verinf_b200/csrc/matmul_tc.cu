@@ -12,18 +12,18 @@
 //
 //  * k_split_rows / k_split_cols write the byte planes K-contiguous: Ap[i][row][k], Bp[j][col][k]
 //    (the second through a shared-memory transpose), zero padded to tile multiples.
-//  * k_matmul_planes: CTA tile 64 x 32 outputs, 8 warps of 16 x 16, k in slices of 32 bytes
-//    through a 3-stage cp.async pipeline; fragments by ldmatrix, products by
-//    mma.sync.m16n8k32.s32.u8.u8.s32 (128 per warp and slice).  Rows of a slice are padded to
-//    48 bytes in shared memory so that ldmatrix is free of bank conflicts.
+//  * k_matmul_planes: CTA tile 64 x 32 outputs, 8 warps of 16 x 16, k in slices of 64 bytes
+//    through a 3-stage cp.async pipeline (one barrier per slice); fragments by ldmatrix, products by
+//    mma.sync.m16n8k32.s32.u8.u8.s32 (256 per warp and slice).  Rows of a slice are padded to
+//    80 bytes in shared memory so that ldmatrix is free of bank conflicts.
 #include "../../include/verinf_b200.h"
 #include "common.cuh"
 #include "gl.cuh"
 
 namespace {
 
-constexpr int TC_TM = 64, TC_TN = 32, TC_KS = 32;      // CTA tile and k slice (bytes per plane row)
-constexpr int TC_ROWB = 48;                             // shared-memory bytes per plane row of a slice
+constexpr int TC_TM = 64, TC_TN = 32, TC_KS = 64;      // CTA tile and k slice (bytes per plane row)
+constexpr int TC_ROWB = 80;                             // shared-memory bytes per plane row of a slice
 constexpr int TC_STAGES = 3;
 constexpr int TC_A_BYTES = 8 * TC_TM * TC_ROWB, TC_B_BYTES = 8 * TC_TN * TC_ROWB;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
@@ -133,16 +133,16 @@ __global__ void __launch_bounds__(256, 1) k_matmul_planes(const uint8_t* __restr
         uint8_t* sa = tc_smem + stage * TC_STAGE_BYTES;
         uint8_t* sb = sa + TC_A_BYTES;
         const int64_t k0 = s * TC_KS;
-        // A: 8 planes x 64 rows x 2 chunks of 16 bytes = 1024 chunks, 4 per thread
+        // A: 8 planes x 64 rows x 4 chunks of 16 bytes = 2048 chunks, 8 per thread
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int e = tid + 256 * q, ch = e & 1, r = (e >> 1) & 63, pl = e >> 7;
+        for (int q = 0; q < 8; ++q) {
+            const int e = tid + 256 * q, ch = e & 3, r = (e >> 2) & 63, pl = e >> 8;
             cp_async16(sa + (pl * TC_TM + r) * TC_ROWB + ch * 16, Ap + ((int64_t)pl * m_pad + row0 + r) * k_pad + k0 + ch * 16);
         }
-        // B: 8 planes x 32 columns x 2 chunks = 512 chunks, 2 per thread
+        // B: 8 planes x 32 columns x 4 chunks = 1024 chunks, 4 per thread
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int e = tid + 256 * q, ch = e & 1, r = (e >> 1) & 31, pl = e >> 6;
+        for (int q = 0; q < 4; ++q) {
+            const int e = tid + 256 * q, ch = e & 3, r = (e >> 2) & 31, pl = e >> 7;
             cp_async16(sb + (pl * TC_TN + r) * TC_ROWB + ch * 16, Bp + ((int64_t)pl * n_pad + col0 + r) * k_pad + k0 + ch * 16);
         }
         cp_async_commit();
@@ -165,23 +165,27 @@ __global__ void __launch_bounds__(256, 1) k_matmul_planes(const uint8_t* __restr
             for (int t = 0; t < 2; ++t)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) acc[s][t][q] = 0;
-        // prologue: slices c0k, c0k+1 in flight
+        // prologue: slices c0k, c0k+1 in flight; one barrier per slice: after it every warp has finished
+        // the previous slice, so its stage can take slice s+2 while slice s is multiplied
         load_slice(c0k, 0);
         if (c0k + 1 < c1k) load_slice(c0k + 1, 1); else cp_async_commit();
         for (int64_t s = c0k; s < c1k; ++s) {
             const int stage = (int)((s - c0k) % TC_STAGES);
-            if (s + 2 < c1k) load_slice(s + 2, (int)((s - c0k + 2) % TC_STAGES)); else cp_async_commit();
-            cp_async_wait<2>();
+            cp_async_wait<1>();
             __syncthreads();
+            if (s + 2 < c1k) load_slice(s + 2, (int)((s - c0k + 2) % TC_STAGES)); else cp_async_commit();
             const uint8_t* sa = tc_smem + stage * TC_STAGE_BYTES;
             const uint8_t* sb = sa + TC_A_BYTES;
-            uint32_t b[8][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ldmatrix_x4(b[j], sb + j * (TC_TN * TC_ROWB) + b_off);
-            mma_planes<0>(acc, sa + a_off, b);
-            __syncthreads();
+            for (int h = 0; h < TC_KS / 32; ++h) {
+                uint32_t b[8][4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ldmatrix_x4(b[j], sb + j * (TC_TN * TC_ROWB) + b_off + h * 32);
+                mma_planes<0>(acc, sa + a_off + h * 32, b);
+            }
         }
         cp_async_wait<0>();
+        __syncthreads();          // the next chunk's prologue overwrites stages 0 and 1
         // fold this chunk: acc[s][t][q] is output (row g (+8 for q >= 2), column 8t + 2 tig + (q & 1))
 #pragma unroll
         for (int t = 0; t < 2; ++t)
