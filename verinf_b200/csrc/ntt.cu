@@ -198,7 +198,6 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     const int ncols_tile = a.ncols - col0 < C ? (int)(a.ncols - col0) : C;   // valid columns of this tile
     const uint32_t ncols32 = (uint32_t)a.ncols;
     uint64_t v[EPT];
-
     if constexpr (MODE == 0) {
         if (a.src_kind == SRC_PLAIN) {
             const uint64_t* src = a.in + item * a.in_item + colg * (int64_t)a.in_col;
@@ -254,9 +253,16 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     } else {
         const int nthr = blockDim.x;
         const uint64_t* src = a.in + item * a.in_item + col0 * (int64_t)a.in_col;
-        for (int e = tid; e < L * C; e += nthr) {
-            int idx = e & (L - 1), cl = e >> LOGL;
-            sm[idx * CP + cl] = cl < ncols_tile ? src[(uint32_t)cl * a.in_col + (uint32_t)idx * a.in_idx] : 0;
+        if (LOGL >= 4 && a.logC == 4) {
+            // 16 columns: the block has L threads, thread tid loads index tid of every column
+            const uint64_t* p = src + (uint32_t)tid * a.in_idx;
+#pragma unroll
+            for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = cl < ncols_tile ? p[(uint32_t)cl * a.in_col] : 0;
+        } else {
+            for (int e = tid; e < L * C; e += nthr) {
+                int idx = e & (L - 1), cl = e >> LOGL;
+                sm[idx * CP + cl] = cl < ncols_tile ? src[(uint32_t)cl * a.in_col + (uint32_t)idx * a.in_idx] : 0;
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -407,9 +413,15 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     {
         const int nthr = blockDim.x;
         const uint64_t* src = a.s1 + item * a.K + col0 * L;
-        for (int e = tid; e < L * C; e += nthr) {
-            int idx = e & (L - 1), cl = e >> LOGL;
-            sm[idx * CP + cl] = cl < ncols_tile ? src[(uint32_t)(cl * L + idx)] : 0;
+        if (LOGL >= 4 && a.logC == 4) {
+            // 16 columns: the block has L threads, thread tid loads index tid of every column
+#pragma unroll
+            for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = cl < ncols_tile ? src[cl * L + tid] : 0;
+        } else {
+            for (int e = tid; e < L * C; e += nthr) {
+                int idx = e & (L - 1), cl = e >> LOGL;
+                sm[idx * CP + cl] = cl < ncols_tile ? src[(uint32_t)(cl * L + idx)] : 0;
+            }
         }
         __syncthreads();
     }

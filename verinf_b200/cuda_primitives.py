@@ -250,15 +250,19 @@ def poly_add(a, b):
 def poly_mul_batched(A, B):
     """Row-wise poly_mul of two (m, d) coefficient matrices -> (m, 2d-1)."""
     assert A.dim() == 2 and B.dim() == 2 and A.shape == B.shape
+    A, B = A.contiguous(), B.contiguous()
+    _chk_u64(A, "A"); _chk_u64(B, "B")
     d = A.size(1)
+    if A.size(0) == 0 or d == 0:
+        return torch.empty((A.size(0), max(2 * d - 1, 0)), dtype=_U64, device=A.device)
     out_len = 2 * d - 1
     n = _next_pow2(out_len)
-    fa, fb = _padded(A, n), _padded(B, n)
-    ntt_forward_batched(fa)
-    ntt_forward_batched(fb)
-    prod = gl_mul(fa, fb)
-    ntt_inverse_batched(prod)
-    return prod[:, :out_len].contiguous()
+    from .fold import ntt_forward_padded          # zero extension inside the transform, no padded copies
+    fa, fb = ntt_forward_padded(A, n), ntt_forward_padded(B, n)
+    with torch.cuda.device(A.device):
+        check(LIB.vi_gl_binary(0, ptr(fa), ptr(fb), ptr(fa), fa.numel(), stream_ptr()))     # in place
+    ntt_inverse_batched(fa)
+    return fa[:, :out_len].contiguous()
 
 
 # ---- linear algebra mod P ----------------------------------------------------------------
