@@ -610,6 +610,18 @@ def test_more_rows_than_a_grid_dimension(cp):
     assert np.array_equal(leaves.cpu().numpy(), oracle.hash_columns(host(codes)))
 
 
+@pytest.mark.parametrize("m,k,n", [(1, 1000, 70), (1, 4096, 16384), (2, 300, 33), (3, 129, 1), (4, 2048, 100), (1, 7, 5),
+                                   (200, 513, 1), (1, 1, 1)])
+def test_matmul_thin_shapes(cp, m, k, n):
+    """row combinations (m <= 4) and single-column products take their own kernels"""
+    rng = np.random.default_rng(m * 1000 + k + n)
+    A, B = rnd_field(rng, (m, k)), rnd_field(rng, (k, n))
+    assert np.array_equal(host(cp.gl_matmul(dev(A), dev(B))), oracle.gl_matmul(A, B))
+    A[:] = np.uint64(0xFFFFFFFEFFFFFFFF)
+    B[:] = np.uint64(P - 1)
+    assert np.array_equal(host(cp.gl_matmul(dev(A), dev(B))), oracle.gl_matmul(A, B))
+
+
 def _matmul_tc(A, B):
     from verinf_b200._lib import LIB, check, ptr, stream_ptr
     m, k = A.shape

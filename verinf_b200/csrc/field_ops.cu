@@ -178,6 +178,40 @@ __global__ void __launch_bounds__(256, VI_MM_MINB) k_matmul(const uint64_t* __re
         }
 }
 
+// Thin product: M <= 4 rows of A against a tall B (k x n), out[mi][j] = sum_i A[mi][i] B[i][j].
+// This is the random linear combination of matrix rows (q_irs accumulation, prover/core.py:1351-1379;
+// combine_t, layergkr/gpu.py:301-308), which must stream B once: a CTA owns 32 columns, its 8 row
+// lanes take the rows i = lane, lane + 8, ... (every warp reads 256 contiguous bytes per row) with
+// unreduced 160-bit sums, and the 8 partial sums meet in shared memory.
+template <int M>
+__global__ void __launch_bounds__(256) k_matmul_thin(const uint64_t* __restrict__ A, const uint64_t* __restrict__ B,
+                                                     uint64_t* __restrict__ C, int64_t k, int64_t n) {
+    __shared__ uint64_t red[8][M][32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t j = (int64_t)blockIdx.x * 32 + tx;
+    uint32_t acc[M][5];
+#pragma unroll
+    for (int mi = 0; mi < M; ++mi)
+#pragma unroll
+        for (int l = 0; l < 5; ++l) acc[mi][l] = 0;
+    if (j < n) {
+        for (int64_t i = ty; i < k; i += 8) {
+            const uint64_t b = B[i * n + j];
+#pragma unroll
+            for (int mi = 0; mi < M; ++mi) mac160(acc[mi], __ldg(A + mi * k + i), b);
+        }
+    }
+#pragma unroll
+    for (int mi = 0; mi < M; ++mi) red[ty][mi][tx] = reduce160(acc[mi]);
+    __syncthreads();
+    if (ty < M && j < n) {
+        uint64_t v = 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) v = add(v, red[r][ty][tx]);
+        C[(int64_t)ty * n + j] = v;
+    }
+}
+
 // Weighted product column sum: part[s][j] = sum over the rows i of split s of
 // w[i] * EA[ia[i]][j] * EB[ib[i]][j].  One thread per column (coalesced rows), products summed
 // unreduced in five 32-bit limbs, one reduction per thread at the end; k_colsum_finish adds the
@@ -400,6 +434,21 @@ extern "C" int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, i
     VI_REQUIRE(A && B && C || k == 0, "gl_matmul: null pointer");
     VI_REQUIRE(C != A && C != B, "gl_matmul: the output must not alias an input");
     VI_REQUIRE(k < (int64_t(1) << 32), "gl_matmul: inner dimension must be below 2^32");
+    if (n == 1 && k > 0) {                     // a single column of B is a vector: matrix-vector product
+        int64_t g = (m * 32 + 255) / 256;
+        VI_REQUIRE(g <= 0x7FFFFFFFLL, "gl_matmul: too many rows");
+        k_matvec<<<(unsigned)g, 256, 0, (cudaStream_t)stream>>>(A, B, C, m, k);
+        return vi::check_launch("k_matvec");
+    }
+    if (m <= 4 && k > 0 && (n + 31) / 32 <= 0x7FFFFFFFLL) {     // linear combination of the rows of B
+        const unsigned g = (unsigned)((n + 31) / 32);
+        cudaStream_t st = (cudaStream_t)stream;
+        if (m == 1) k_matmul_thin<1><<<g, 256, 0, st>>>(A, B, C, k, n);
+        else if (m == 2) k_matmul_thin<2><<<g, 256, 0, st>>>(A, B, C, k, n);
+        else if (m == 3) k_matmul_thin<3><<<g, 256, 0, st>>>(A, B, C, k, n);
+        else k_matmul_thin<4><<<g, 256, 0, st>>>(A, B, C, k, n);
+        return vi::check_launch("k_matmul_thin");
+    }
     dim3 grid((unsigned)((n + MM_TN - 1) / MM_TN), (unsigned)((m + MM_TM - 1) / MM_TM));
     VI_REQUIRE(grid.y <= 65535, "gl_matmul: too many rows for one launch (m <= 4194240)");
     VI_CUDA(cudaFuncSetAttribute(k_matmul, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM));

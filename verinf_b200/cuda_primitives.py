@@ -278,7 +278,7 @@ def gl_matmul(A, B, force_simt=False):
     m, k, n = A.size(0), A.size(1), B.size(1)
     Cm = torch.empty((m, n), dtype=_U64, device=A.device)
     with torch.cuda.device(A.device):
-        if m * k * n >= _TC_MIN_MACS and not force_simt:
+        if m > 4 and n > 1 and m * k * n >= _TC_MIN_MACS and not force_simt:
             # large products: byte planes on the integer tensor cores (same result)
             nb = LIB.vi_gl_matmul_tc_scratch_bytes(m, k, n)
             sc = scratch(nb, A.device, "matmul")
