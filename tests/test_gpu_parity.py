@@ -831,3 +831,35 @@ def test_commit_host_equals_device_commit(cp, rows, slices):
     padded[:, :ell] = msg
     padded[:, ell:] = oracle.row_prg(bytes(range(32)), 9, rows, k - ell)
     assert oracle.commit_rows(padded, n) == want
+
+
+# ---------------------------------------------------------------- layergkr helpers ----
+def test_layergkr_helper_mirrors(cp, golden):
+    """the helpers of layergkr/gpu.py around the hot path: same values as their definitions"""
+    from types import SimpleNamespace
+    from verinf_b200 import layergkr_gpu as lg
+    g = golden.encode_vectors
+    cfg = SimpleNamespace(ELL=16, K_DEG=32, N_LIG=128)
+    msg = g["msg_16_32_128"]
+    rows = [[int(v) for v in r] for r in msg]
+    want = g["code_16_32_128"]
+    assert lg.available()
+    assert np.array_equal(np.array(lg.encode_batch(cfg, rows), dtype=np.uint64), want)
+    codes = lg.encode_batch_t(cfg, rows)
+    assert np.array_equal(host(codes), want)
+    rng = np.random.default_rng(2)
+    coeffs = [int(v) for v in rnd_field(rng, msg.shape[0])]
+    comb = [sum(c * int(want[i, j]) for i, c in enumerate(coeffs)) % P for j in range(128)]
+    assert [int(v) for v in host(lg.combine_t(cfg, codes, coeffs))[0]] == comb
+    assert lg.linear_combination(cfg, [[int(v) for v in r] for r in want], coeffs) == comb
+    assert lg.column(codes, 77) == [int(v) for v in want[:, 77]]
+    root, levels = lg.hash_and_tree(cfg, codes)
+    assert root == g["root_16_32_128"].tobytes()
+    assert b"".join(b"".join(l) for l in lg.levels_to_host(levels)) == g["tree_16_32_128"].tobytes()
+    for n in (1, 7, 1024, 1025, 100003):
+        v = rnd_field(rng, n)
+        assert int(host(lg.gl_sum(dev(v)))[0]) == sum(int(x) for x in v) % P
+    f = rnd_field(rng, 4096)
+    r = int(rnd_field(rng, 1)[0])
+    got = host(lg.fold_t(dev(f), dev(np.array([r], dtype=np.uint64))))
+    assert [int(x) for x in got] == [(int(a) + r * (int(b) - int(a))) % P for a, b in zip(f[:2048], f[2048:])]

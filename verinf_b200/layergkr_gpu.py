@@ -1,6 +1,8 @@
-"""Device-resident versions of the three layergkr/gpu.py entry points that sit on the hot
-path: `encode_batch_ntt`, `hash_and_tree`, `prove_terms_gpu` (same names, argument meaning
-and return values as layergkr/gpu.py:141-203, 274-289, 350-410).
+"""Device-resident versions of the layergkr/gpu.py entry points (same names, argument meaning
+and return values): `encode_batch_ntt`, `hash_and_tree`, `prove_terms_gpu` on the hot path
+(layergkr/gpu.py:141-203, 274-289, 350-410) and the helpers around them (`encode_batch`,
+`encode_batch_t`, `linear_combination`, `combine_t`, `column`, `levels_to_host`, `gl_sum`,
+`fold_t`, layergkr/gpu.py:92-126, 256-347), so the module can stand in for layergkr.gpu.
 
 `prove_terms_gpu` keeps the reference's per-round `coin` callback, but each round is one
 fused fold+evaluate launch and one small D2H copy of the deg+1 samples, instead of ~10
@@ -33,6 +35,87 @@ def hash_and_tree(cfg, mat):
     dig = cp.hash_columns_streamed(mat.contiguous())
     root_t, levels_t = cp.merkle_build_blake3(dig)
     return bytes(root_t.cpu().tolist()), levels_t
+
+
+def available() -> bool:
+    """True when the CUDA library is loaded and a device is present (layergkr/gpu.py:76-77)."""
+    return torch.cuda.is_available()
+
+
+def _messages_tensor(cfg, messages):
+    if hasattr(messages, "shape"):
+        return messages.contiguous()
+    src = [[int(v) % P for v in m] + [0] * (cfg.ELL - len(m)) for m in messages]
+    return torch.tensor(src, dtype=torch.uint64, device="cuda")
+
+
+def encode_batch_t(cfg, messages):
+    """Encode to a device tensor (layergkr/gpu.py:256-271).  The reference multiplies by the
+    ELL x N Lagrange matrix; the NTT route gives the same codewords (the equivalence the
+    reference pins in selftest_ntt, layergkr/gpu.py:206-253) without building that matrix."""
+    return encode_batch_ntt(cfg, _messages_tensor(cfg, messages))
+
+
+def encode_batch(cfg, messages) -> List[List[int]]:
+    """Encode and return Python rows (layergkr/gpu.py:92-110)."""
+    codes = encode_batch_t(cfg, messages)
+    return [[int(v) for v in row] for row in codes.view(torch.int64).cpu().numpy().view(np.uint64).tolist()]
+
+
+def combine_t(cfg, mat, coeffs: Sequence[int]):
+    """sum_i coeffs[i] * mat[i] as a (1, N) device tensor (layergkr/gpu.py:301-308); the matrix is
+    streamed once by the thin-product kernel."""
+    A = torch.tensor([[int(c) % P for c in coeffs]], dtype=torch.uint64, device=mat.device)
+    return cp.gl_matmul(A, mat.contiguous())
+
+
+def linear_combination(cfg, codewords, coeffs: Sequence[int]) -> List[int]:
+    """sum_i coeffs[i] * codewords[i] for Python rows (layergkr/gpu.py:113-123)."""
+    B = torch.tensor([[int(v) % P for v in c] for c in codewords], dtype=torch.uint64, device="cuda")
+    out = combine_t(cfg, B, coeffs)[0]
+    return [int(v) for v in out.view(torch.int64).cpu().numpy().view(np.uint64).tolist()]
+
+
+def column(mat, col: int) -> List[int]:
+    """One codeword column on the host (layergkr/gpu.py:311-316)."""
+    from .commit import open_columns
+    out = open_columns(mat.contiguous(), [int(col)])[0]
+    return [int(v) for v in out.view(torch.int64).cpu().numpy().view(np.uint64).tolist()]
+
+
+def levels_to_host(levels_t) -> List[List[bytes]]:
+    """The whole tree as host byte strings (layergkr/gpu.py:292-298).  For the T opening paths
+    alone `commit.merkle_paths` moves T*depth*33 bytes instead."""
+    out = []
+    for lvl in levels_t:
+        arr = lvl.cpu().numpy()
+        out.append([arr[r].tobytes() for r in range(arr.shape[0])])
+    return out
+
+
+def gl_sum(t):
+    """Field sum of a device vector as a 1-element tensor (layergkr/gpu.py:326-338): one thin
+    product with a row of ones per 1024 columns, then the 1024 partial sums the same way."""
+    v = t.reshape(-1).contiguous()
+    while v.numel() > 1:
+        n = v.numel()
+        cols = 1024 if n > 1024 else 1
+        rows = -(-n // cols)
+        if rows * cols != n:
+            pad = torch.zeros(rows * cols, dtype=torch.int64, device=v.device)
+            pad[:n] = v.view(torch.int64)
+            v = pad.view(torch.uint64)
+        ones = torch.ones((1, rows), dtype=torch.int64, device=v.device).view(torch.uint64)
+        v = cp.gl_matmul(ones, v.view(torch.int64).view(rows, cols).view(torch.uint64)).reshape(-1)
+    return v
+
+
+def fold_t(f, r_t):
+    """(f[:h] + r*(f[h:] - f[:h])) mod p on the device (layergkr/gpu.py:341-347); r_t is a
+    1-element tensor."""
+    h = f.numel() // 2
+    lo, hi = f[:h].contiguous(), f[h:2 * h].contiguous()
+    return cp.gl_add(lo, cp.gl_mul_rowvec(cp.gl_sub(hi, lo).reshape(h, 1), r_t.reshape(1)).reshape(h))
 
 
 class SumcheckProblem:
