@@ -47,10 +47,16 @@ int vi_gl_axpy(uint64_t* y, uint64_t alpha, const uint64_t* x, int64_t n, void* 
  * prover/kernels/ntt.cuh:310-770).  In place over m contiguous rows of length n
  * (power of two, 2 <= n <= 2^24), natural order in and out; the inverse scales by
  * n^-1.  Transforms longer than 1024 need scratch (any size >= n*8 bytes works;
- * vi_ntt_scratch_bytes gives the size that keeps a row chunk L2-resident). */
+ * vi_ntt_scratch_bytes gives the recommended size: the rows of a 1 GiB chunk). */
 int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n);
 int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
                    void* scratch, int64_t scratch_bytes, void* stream);
+
+/* The library owns only immutable per-device tables (twiddles, four-step factors, coset
+ * scalings), built on the first use of a length and kept for the life of the process, as the
+ * reference keeps its twiddle contexts (prover/cuda_primitives.py:319-331).  vi_release_tables
+ * frees them all; call it with no library kernel in flight. */
+int vi_release_tables(void);
 
 /* ---- Reed-Solomon row encode ---------------------------------------------------
  * replaces encode_messages + _coset_encode_codewords (prover/core.py:721-802) and

@@ -863,3 +863,19 @@ def test_layergkr_helper_mirrors(cp, golden):
     r = int(rnd_field(rng, 1)[0])
     got = host(lg.fold_t(dev(f), dev(np.array([r], dtype=np.uint64))))
     assert [int(x) for x in got] == [(int(a) + r * (int(b) - int(a))) % P for a, b in zip(f[:2048], f[2048:])]
+
+
+def test_release_tables_then_reuse(cp):
+    """tables are rebuilt after vi_release_tables: same transform before and after"""
+    from verinf_b200._lib import LIB, check
+    rng = np.random.default_rng(3)
+    a = rnd_field(rng, (3, 4096))
+    x = dev(a)
+    cp.ntt_forward_batched(x)
+    torch.cuda.synchronize()
+    check(LIB.vi_release_tables())
+    y = dev(a)
+    cp.ntt_forward_batched(y)
+    assert torch.equal(x.view(torch.int64), y.view(torch.int64))
+    _, c = cp.encode_rows(dev(a[:, :1000]), 4096, 16384)
+    assert np.array_equal(host(c)[0], oracle.encode_rows(np.concatenate([a[:1, :1000], np.zeros((1, 3096), np.uint64)], 1), 16384)[1][0])

@@ -40,6 +40,7 @@ SIGNATURES = {
     "vi_merkle_upper_nodes": (_i64, [_i64]),
     "vi_merkle_build": (_int, [_p, _i64, _p, _p]),
     "vi_merkle_level": (_int, [_p, _i64, _p, _p]),
+    "vi_release_tables": (_int, []),
     "vi_ntt_forward_padded": (_int, [_p, _i64, _i64, _p, _i64, _p, _i64, _p]),
     "vi_product_colsum_scratch_bytes": (_i64, [_i64, _i64]),
     "vi_product_colsum": (_int, [_p, _p, _i64, _p, _p, _p, _i64, _p, _int, _p, _i64, _p]),

@@ -701,6 +701,25 @@ int64_t chunk_bytes() {
 
 }  // namespace
 
+// Frees every twiddle / four-step / twist table this library allocated (all devices).  No kernel of
+// the library may be in flight; the tables are rebuilt on the next use of a length.
+extern "C" int vi_release_tables(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int cur = 0;
+    VI_CUDA(cudaGetDevice(&cur));
+    for (auto& kv : g_tables) {
+        VI_CUDA(cudaSetDevice(kv.first));
+        VI_CUDA(cudaDeviceSynchronize());
+        for (auto& t : kv.second.tw) cudaFree(t.second);
+        for (auto& t : kv.second.twist) cudaFree(t.second);
+        for (auto& t : kv.second.fs) cudaFree(t.second);
+        for (auto& t : kv.second.cscale) cudaFree(t.second);
+    }
+    g_tables.clear();
+    VI_CUDA(cudaSetDevice(cur));
+    return VI_OK;
+}
+
 extern "C" int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n) {
     if (n <= (int64_t(1) << SINGLE_LOGL) || m <= 0) return 0;
     int64_t row = n * 8;
