@@ -210,12 +210,16 @@ int vi_kquant_encode_rows(const uint8_t* raw, int qtype, double S, int64_t d_out
  * prod_{j < nfac[t]} table[fac[t*4 + j]]  (at most 8 tables, 8 terms, 4 factors).
  * coefs, nfac and fac are small HOST arrays (n_terms, n_terms, n_terms*4 entries).
  *   vi_sumcheck_claim   sum over the hypercube of all terms -> out[0]
- *   vi_sumcheck_round   if fold != 0 first folds every table with challenge r
+ *   vi_sumcheck_round   flags bit 0 (fold): first folds every table with challenge r
  *                       (f'[i] = f[i] + r*(f[half+i] - f[i]), size -> size/2, in place),
  *                       then writes the round samples g(0..deg) of the (folded) tables
  *                       to out[0..deg].  `size` is the table length BEFORE the fold.
  *                       With size/2 == 1 after folding no samples exist; the final
  *                       values are tables[k*stride].
+ *                       flags bit 1 (skip x = 1): out[1] is not computed (written as 0); the
+ *                       caller derives it from g(0) + g(1) = g_prev(r), the value of the
+ *                       previous round polynomial at its challenge (the sum of the terms over
+ *                       the hypercube for the first round).  One product fewer per table pair.
  * partials: scratch of vi_sumcheck_scratch_bytes() bytes.  out: device, >= 8 u64. */
 int64_t vi_sumcheck_scratch_bytes(void);
 int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_tables, int64_t size,
@@ -223,13 +227,15 @@ int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_tables, int6
                       uint64_t* out, void* partials, void* stream);
 /* All rounds for challenges known up front (HOST array coins[n_rounds], size = 2^n_rounds): queues
  * every fold+evaluate launch without a host round trip; samples (device, n_rounds x 8 u64) receives
- * g(0..deg) of round i at samples[8*i ..].  Equivalent to n_rounds + 1 calls of vi_sumcheck_round. */
+ * g(0..deg) of round i at samples[8*i ..], EXCEPT g(1) of rounds i >= 1, which is left 0 and
+ * follows from g_i(0) + g_i(1) = g_{i-1}(coins[i-1]) (round 0 is complete, so its g(0) + g(1) is
+ * also the claim).  Equivalent to n_rounds + 1 calls of vi_sumcheck_round with flags 0, 3, 3, ..., 1. */
 int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                     int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
                     const uint64_t* coins, int n_rounds, uint64_t* samples, void* partials, void* stream);
 int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                       int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
-                      int fold, uint64_t r, uint64_t* out, void* partials, void* stream);
+                      int flags, uint64_t r, uint64_t* out, void* partials, void* stream);
 
 /* ---- remaining exports of the reference module (not on the hot path) -------------
  * poly_eval (prover/kernels/gl_extras.cuh:93-108), gl_matmul / gl_matvec

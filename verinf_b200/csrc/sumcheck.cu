@@ -61,7 +61,7 @@ __device__ __forceinline__ void block_reduce(uint64_t (&acc)[MAX_SAMPLES], int n
 // MODE 1: round samples on the tables as they are (pairs i, i+half)
 // MODE 2: fold with r (size -> size/2, in place), then round samples of the folded tables
 template <int MODE>
-__global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, uint64_t r, uint64_t* partials) {
+__global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, uint64_t r, int skip1, uint64_t* partials) {
     __shared__ uint64_t slo[MAX_TABLES][BLOCK], sd[MAX_TABLES][BLOCK];
     const int ns = MODE == 0 ? 1 : pb.deg + 1;
     // number of work items: claim = size; plain round = size/2 pairs; fold+round = size/4 pairs of pairs
@@ -100,11 +100,13 @@ __global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, ui
 #pragma unroll
             for (int x = 0; x < MAX_SAMPLES; ++x) {
                 if (x < ns) {
-                    uint64_t prod = cur[0];
+                    if (!(skip1 && x == 1)) {       // g(1) follows from g(0) + g(1) = previous claim
+                        uint64_t prod = cur[0];
 #pragma unroll
-                    for (int k = 1; k < MAX_FAC; ++k)
-                        if (k < pb.n_tables) prod = mul(prod, cur[k]);
-                    acc[x] = add(acc[x], prod);
+                        for (int k = 1; k < MAX_FAC; ++k)
+                            if (k < pb.n_tables) prod = mul(prod, cur[k]);
+                        acc[x] = add(acc[x], prod);
+                    }
 #pragma unroll
                     for (int k = 0; k < MAX_FAC; ++k)
                         if (k < pb.n_tables) cur[k] = add(cur[k], sd[k][tid]);
@@ -122,11 +124,13 @@ __global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, ui
 #pragma unroll
                 for (int x = 0; x < MAX_SAMPLES; ++x) {
                     if (x < ns) {
-                        uint64_t prod = pb.coef[t];
+                        if (!(skip1 && x == 1)) {
+                            uint64_t prod = pb.coef[t];
 #pragma unroll
-                        for (int j = 0; j < MAX_FAC; ++j)
-                            if (j < pb.nfac[t]) prod = mul(prod, cur[j]);
-                        acc[x] = add(acc[x], prod);
+                            for (int j = 0; j < MAX_FAC; ++j)
+                                if (j < pb.nfac[t]) prod = mul(prod, cur[j]);
+                            acc[x] = add(acc[x], prod);
+                        }
 #pragma unroll
                         for (int j = 0; j < MAX_FAC; ++j) cur[j] = add(cur[j], dd[j]);
                     }
@@ -135,6 +139,64 @@ __global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, ui
         }
     }
     block_reduce(acc, ns, partials);
+}
+
+// The common case -- one term, coefficient 1, the product of all NT tables (NT <= 4) -- with the
+// table count known at compile time: the pair values stay in registers (no shared-memory staging,
+// no per-table runtime predicates), which lifts the occupancy limit of the general kernel.
+template <int MODE, int NT>
+__global__ void __launch_bounds__(BLOCK) k_sumcheck_simple(Problem pb, int64_t size, uint64_t r, int skip1,
+                                                           uint64_t* partials) {
+    constexpr int NS = MODE == 0 ? 1 : NT + 1;
+    const int64_t items = MODE == 0 ? size : MODE == 1 ? size / 2 : size / 4;
+    const int64_t q = items;
+    uint64_t acc[MAX_SAMPLES];
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) acc[x] = 0;
+    const int64_t stride = (int64_t)gridDim.x * BLOCK;
+    for (int64_t i = (int64_t)blockIdx.x * BLOCK + threadIdx.x; i < items; i += stride) {
+        uint64_t cur[NT], d[NT];
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+            uint64_t* f = pb.tab[k];
+            uint64_t lo, hi;
+            if (MODE == 0) { lo = f[i]; hi = lo; }
+            else if (MODE == 1) { lo = f[i]; hi = f[i + q]; }
+            else {
+                const uint64_t a0 = f[i], b0 = f[i + q], a1 = f[i + 2 * q], b1 = f[i + 3 * q];
+                lo = add(a0, mul(r, sub(a1, a0)));
+                hi = add(b0, mul(r, sub(b1, b0)));
+                f[i] = lo;
+                f[i + q] = hi;
+            }
+            cur[k] = lo;
+            d[k] = sub(hi, lo);
+        }
+#pragma unroll
+        for (int x = 0; x < NS; ++x) {
+            if (!(skip1 && x == 1)) {
+                uint64_t prod = cur[0];
+#pragma unroll
+                for (int k = 1; k < NT; ++k) prod = mul(prod, cur[k]);
+                acc[x] = add(acc[x], prod);
+            }
+            if (x + 1 < NS) {
+#pragma unroll
+                for (int k = 0; k < NT; ++k) cur[k] = add(cur[k], d[k]);
+            }
+        }
+    }
+    block_reduce(acc, NS, partials);
+}
+
+template <int MODE>
+void launch_simple(const Problem& pb, int g, cudaStream_t st, int64_t size, uint64_t r, int skip1, uint64_t* partials) {
+    switch (pb.n_tables) {
+        case 1: k_sumcheck_simple<MODE, 1><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
+        case 2: k_sumcheck_simple<MODE, 2><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
+        case 3: k_sumcheck_simple<MODE, 3><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
+        default: k_sumcheck_simple<MODE, 4><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
+    }
 }
 
 __global__ void __launch_bounds__(BLOCK) k_sumcheck_finish(const uint64_t* __restrict__ partials, int n_blocks,
@@ -225,14 +287,17 @@ extern "C" int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_t
     cudaStream_t st = (cudaStream_t)stream;
     int g = grid_for(size);
     vi::ProfScope prof(vi::PROF_SUMCHECK, st);
-    k_sumcheck<0><<<g, BLOCK, 0, st>>>(pb, size, 0, (uint64_t*)partials);
+    if (pb.simple) launch_simple<0>(pb, g, st, size, 0, 0, (uint64_t*)partials);
+    else k_sumcheck<0><<<g, BLOCK, 0, st>>>(pb, size, 0, 0, (uint64_t*)partials);
     k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, 1, out);
     return vi::check_launch("k_sumcheck<claim>");
 }
 
 extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                                  int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
-                                 int fold, uint64_t r, uint64_t* out, void* partials, void* stream) {
+                                 int flags, uint64_t r, uint64_t* out, void* partials, void* stream) {
+    const int fold = flags & 1, skip1 = (flags >> 1) & 1;
+    VI_REQUIRE((flags & ~3) == 0, "sumcheck: unknown flag bits");
     Problem pb;
     int rc = make_problem(pb, tables, stride, n_tables, n_terms, coefs, nfac, fac);
     if (rc) return rc;
@@ -244,7 +309,8 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
     vi::ProfScope prof(vi::PROF_SUMCHECK, st);
     if (!fold) {
         int g = grid_for(size / 2);
-        k_sumcheck<1><<<g, BLOCK, 0, st>>>(pb, size, 0, (uint64_t*)partials);
+        if (pb.simple) launch_simple<1>(pb, g, st, size, 0, skip1, (uint64_t*)partials);
+        else k_sumcheck<1><<<g, BLOCK, 0, st>>>(pb, size, 0, skip1, (uint64_t*)partials);
         k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
         return vi::check_launch("k_sumcheck<round>");
     }
@@ -253,7 +319,8 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
         return vi::check_launch("k_final_fold");
     }
     int g = grid_for(size / 4);
-    k_sumcheck<2><<<g, BLOCK, 0, st>>>(pb, size, r, (uint64_t*)partials);
+    if (pb.simple) launch_simple<2>(pb, g, st, size, r, skip1, (uint64_t*)partials);
+    else k_sumcheck<2><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, (uint64_t*)partials);
     k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
     return vi::check_launch("k_sumcheck<fold+round>");
 }
@@ -265,7 +332,8 @@ extern "C" int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, i
     VI_REQUIRE(n_rounds == 0 || (coins && samples), "sumcheck_run: null pointer");
     int64_t cur = size;
     for (int rnd = 0; rnd < n_rounds; ++rnd) {
-        int rc = vi_sumcheck_round(tables, stride, n_tables, cur, n_terms, coefs, nfac, fac, rnd > 0,
+        // rounds after the first skip the sample at x = 1 (flag 2): see the header
+        int rc = vi_sumcheck_round(tables, stride, n_tables, cur, n_terms, coefs, nfac, fac, rnd > 0 ? 3 : 0,
                                    rnd > 0 ? coins[rnd - 1] : 0, samples + (int64_t)rnd * 8, partials, stream);
         if (rc) return rc;
         if (rnd > 0) cur /= 2;

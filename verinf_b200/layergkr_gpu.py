@@ -142,6 +142,7 @@ class SumcheckProblem:
         self._out = torch.empty(8, dtype=torch.uint64, device=dev)
         self._partials = scratch(LIB.vi_sumcheck_scratch_bytes(), dev, "sumcheck")
         self._host = torch.empty(8, dtype=torch.uint64).pin_memory()
+        self._prev = None       # samples of the previous round (to derive g(1) of the next one)
 
     def _args(self):
         return (self.tables.size(1), self.n_tables, self.size, self.n_terms,
@@ -162,14 +163,20 @@ class SumcheckProblem:
         """Fold with r (None on the first round), then return the samples g(0..deg) of the
         current tables, or None once the tables are down to a single entry."""
         fold = r is not None
+        # after the first round g(1) is not computed on the device: g(0) + g(1) = g_prev(r)
+        skip = fold and self._prev is not None
         with torch.cuda.device(self.tables.device):
-            check(LIB.vi_sumcheck_round(ptr(self.tables), *self._args(), int(fold), (r or 0) % P,
-                                        ptr(self._out), ptr(self._partials), stream_ptr()))
+            check(LIB.vi_sumcheck_round(ptr(self.tables), *self._args(), int(fold) | (2 if skip else 0),
+                                        (r or 0) % P, ptr(self._out), ptr(self._partials), stream_ptr()))
         if fold:
             self.size //= 2
         if self.size < 2:
             return None
-        return self._read(self.deg + 1)
+        ys = self._read(self.deg + 1)
+        if skip:
+            ys[1] = (_interp_at(self._prev, r % P) - ys[0]) % P
+        self._prev = ys
+        return ys
 
     def run(self, coins: Sequence[int]):
         """All rounds back to back for challenges known up front (every call site of the reference
@@ -184,10 +191,43 @@ class SumcheckProblem:
                                       ptr(self._partials), stream_ptr()))
         self.size = 1
         host = buf.view(torch.int64).cpu().view(torch.uint64)
-        return [[int(v) for v in row[:self.deg + 1].tolist()] for row in host[:n_rounds]]
+        out = [[int(v) for v in row[:self.deg + 1].tolist()] for row in host[:n_rounds]]
+        for i in range(1, n_rounds):      # g_i(1) = g_{i-1}(coins[i-1]) - g_i(0)
+            out[i][1] = (_interp_at(out[i - 1], int(cs[i - 1])) - out[i][0]) % P
+        self._prev = out[-1] if out else None
+        return out
 
     def finals(self) -> List[int]:
         return [int(v) for v in self.tables[:, 0].cpu().tolist()]
+
+
+_INV_DEN = {}     # n -> [1 / prod_{j != i} (i - j) mod p for i < n]  (Lagrange weights of the nodes 0..n-1)
+
+
+def _interp_at(ys: Sequence[int], r: int) -> int:
+    """Value at r of the polynomial of degree < len(ys) through (0, ys[0]), (1, ys[1]), ..."""
+    n = len(ys)
+    if r < n:
+        return ys[r]
+    inv = _INV_DEN.get(n)
+    if inv is None:
+        inv = []
+        for i in range(n):
+            den = 1
+            for j in range(n):
+                if j != i:
+                    den = den * ((i - j) % P) % P
+            inv.append(pow(den, P - 2, P))
+        _INV_DEN[n] = inv
+    diffs = [(r - j) % P for j in range(n)]
+    total = 0
+    for i, y in enumerate(ys):
+        num = 1
+        for j in range(n):
+            if j != i:
+                num = num * diffs[j] % P
+        total = (total + y * num % P * inv[i]) % P
+    return total
 
 
 def _poly_eval(coeffs, x, p):
@@ -228,12 +268,14 @@ def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=No
     n_rounds = prob.size.bit_length() - 1
     deg = prob.deg
     mu = mu0 % P
-    claim = (prob.claim() + mu) % P
     round_polys, challenges = [], []
-    if coins is not None and mask is None:
+    if coins is not None and mask is None and n_rounds > 0:
         challenges = [int(c) % P for c in coins]
-        round_polys = [list(enumerate(ys)) for ys in prob.run(challenges)]
+        all_ys = prob.run(challenges)
+        claim = (all_ys[0][0] + all_ys[0][1] + mu) % P       # the sum over the hypercube is g_0(0) + g_0(1)
+        round_polys = [list(enumerate(ys)) for ys in all_ys]
         return claim, round_polys, challenges, mu
+    claim = (prob.claim() + mu) % P
     r = None
     for rnd in range(n_rounds):
         ys = prob.round(r)
