@@ -44,9 +44,10 @@ def parse():
     ap.add_argument("--sumcheck", action="store_true", help="also time the 2^24 degree-3 sumcheck")
     ap.add_argument("--extra", action="store_true",
                     help="also run the secondary workloads: fused K-quant lift+encode, 7B-layer commit+sumcheck")
-    ap.add_argument("--micro", choices=["matmul", "fold"],
-                    help="run only a small case of one secondary kernel (1024 x 2048 x 2048 matmul, or the fold "
-                         "of 1024 row pairs at K = 16384) and print its figures; the case the ncu summaries use")
+    ap.add_argument("--micro", choices=["matmul", "fold", "sumcheck"],
+                    help="run only one secondary kernel (1024 x 2048 x 2048 matmul, the fold of 1024 row pairs "
+                         "at K = 16384, or the 2^24 x 3 degree-3 sumcheck) and print its figures; the cases the ncu "
+                         "summaries use")
     return ap.parse_args()
 
 
@@ -352,7 +353,12 @@ def run_micro(a):
     from verinf_b200 import workloads
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    out = workloads.field_matmul(dev, 1024, 2048, 2048) if a.micro == "matmul" else workloads.fold_products(dev)
+    if a.micro == "matmul":
+        out = workloads.field_matmul(dev, 1024, 2048, 2048)
+    elif a.micro == "fold":
+        out = workloads.fold_products(dev)
+    else:
+        out = time_sumcheck(torch, dev)
     print(json.dumps({"micro": a.micro, **out}))
 
 
