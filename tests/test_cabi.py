@@ -146,3 +146,25 @@ def test_python_wrappers_reject_bad_tensors_before_any_launch(lib):
         cp.hash_columns_streamed(cpu_t.reshape(2, 4))
     with pytest.raises(AssertionError):
         cp.MerkleColumnAccumulator(16, 128)
+
+
+def test_round_sample_derivation_host_logic():
+    """g(1) of a sumcheck round is derived on the host from the previous round's samples:
+    check the Lagrange evaluation and the identity g_k(0) + g_k(1) = g_{k-1}(r) against the oracle"""
+    import numpy as np
+    import oracle
+    from verinf_b200.layergkr_gpu import _interp_at, P
+    rng = np.random.default_rng(0)
+    coeffs = [int(v) for v in rng.integers(0, P, size=4, dtype=np.uint64)]
+    poly = lambda x: sum(c * pow(x, i, P) for i, c in enumerate(coeffs)) % P
+    ys = [poly(x) for x in range(4)]
+    for r in (0, 3, 4, 12345678901234567, P - 1):
+        assert _interp_at(ys, r) == poly(r)
+    assert _interp_at([7], 99) == 7
+    tabs = rng.integers(0, P, size=(3, 64), dtype=np.uint64)
+    coins = [int(c) for c in rng.integers(0, P, size=6, dtype=np.uint64)]
+    claim, samples, _ = oracle.sumcheck(tabs, [(1, [0, 1, 2])], coins)
+    assert (int(samples[0][0]) + int(samples[0][1])) % P == claim
+    for k in range(1, 6):
+        prev = [int(v) for v in samples[k - 1][:4]]
+        assert (int(samples[k][0]) + int(samples[k][1])) % P == _interp_at(prev, coins[k - 1])

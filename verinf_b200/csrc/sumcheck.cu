@@ -62,7 +62,11 @@ __device__ __forceinline__ void block_reduce(uint64_t (&acc)[MAX_SAMPLES], int n
 // MODE 2: fold with r (size -> size/2, in place), then round samples of the folded tables
 template <int MODE>
 __global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, uint64_t r, int skip1, uint64_t* partials) {
-    __shared__ uint64_t slo[MAX_TABLES][BLOCK], sd[MAX_TABLES][BLOCK];
+    // pair values of this thread for every table, staged for the runtime term structure:
+    // 2 * n_tables * BLOCK words of dynamic shared memory
+    extern __shared__ uint64_t sc_smem[];
+    uint64_t (*slo)[BLOCK] = reinterpret_cast<uint64_t (*)[BLOCK]>(sc_smem);
+    uint64_t (*sd)[BLOCK] = reinterpret_cast<uint64_t (*)[BLOCK]>(sc_smem + (size_t)pb.n_tables * BLOCK);
     const int ns = MODE == 0 ? 1 : pb.deg + 1;
     // number of work items: claim = size; plain round = size/2 pairs; fold+round = size/4 pairs of pairs
     const int64_t items = MODE == 0 ? size : MODE == 1 ? size / 2 : size / 4;
@@ -266,6 +270,8 @@ int make_problem(Problem& pb, uint64_t* tables, int64_t stride, int n_tables, in
     return VI_OK;
 }
 
+size_t general_smem(const Problem& pb) { return (size_t)2 * pb.n_tables * BLOCK * sizeof(uint64_t); }
+
 int grid_for(int64_t items) {
     int64_t g = (items + BLOCK - 1) / BLOCK;
     if (g < 1) g = 1;
@@ -288,7 +294,7 @@ extern "C" int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_t
     int g = grid_for(size);
     vi::ProfScope prof(vi::PROF_SUMCHECK, st);
     if (pb.simple) launch_simple<0>(pb, g, st, size, 0, 0, (uint64_t*)partials);
-    else k_sumcheck<0><<<g, BLOCK, 0, st>>>(pb, size, 0, 0, (uint64_t*)partials);
+    else k_sumcheck<0><<<g, BLOCK, general_smem(pb), st>>>(pb, size, 0, 0, (uint64_t*)partials);
     k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, 1, out);
     return vi::check_launch("k_sumcheck<claim>");
 }
@@ -310,7 +316,7 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
     if (!fold) {
         int g = grid_for(size / 2);
         if (pb.simple) launch_simple<1>(pb, g, st, size, 0, skip1, (uint64_t*)partials);
-        else k_sumcheck<1><<<g, BLOCK, 0, st>>>(pb, size, 0, skip1, (uint64_t*)partials);
+        else k_sumcheck<1><<<g, BLOCK, general_smem(pb), st>>>(pb, size, 0, skip1, (uint64_t*)partials);
         k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
         return vi::check_launch("k_sumcheck<round>");
     }
@@ -320,7 +326,7 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
     }
     int g = grid_for(size / 4);
     if (pb.simple) launch_simple<2>(pb, g, st, size, r, skip1, (uint64_t*)partials);
-    else k_sumcheck<2><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, (uint64_t*)partials);
+    else k_sumcheck<2><<<g, BLOCK, general_smem(pb), st>>>(pb, size, r, skip1, (uint64_t*)partials);
     k_sumcheck_finish<<<1, BLOCK, 0, st>>>((const uint64_t*)partials, g, pb.deg + 1, out);
     return vi::check_launch("k_sumcheck<fold+round>");
 }
