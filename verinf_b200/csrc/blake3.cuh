@@ -111,6 +111,39 @@ __device__ __forceinline__ uint64_t pad_prg(const uint32_t (&seed)[8], uint64_t 
 }
 
 
+// The pad PRG hashes seed32 || row_le8 || k_le8: of the 8 G functions of the first round only one
+// (words 1, 6, 11, 12 with the message words holding k) depends on k.  pad_prg_prefix computes
+// the state after the other seven once per (seed, row); pad_prg_from finishes an element from it.
+__device__ __forceinline__ void pad_prg_prefix(const uint32_t (&seed)[8], uint64_t row, uint32_t (&v)[16]) {
+    v[0] = IV0; v[1] = IV1; v[2] = IV2; v[3] = IV3; v[4] = IV4; v[5] = IV5; v[6] = IV6; v[7] = IV7;
+    v[8] = IV0; v[9] = IV1; v[10] = IV2; v[11] = IV3;
+    v[12] = 0; v[13] = 0; v[14] = 48; v[15] = CHUNK_START | CHUNK_END | ROOT;
+    const uint32_t r0 = (uint32_t)row, r1 = (uint32_t)(row >> 32), z = 0;
+    VB3_G(v[0], v[4], v[8], v[12], seed[0], seed[1]);
+    VB3_G(v[1], v[5], v[9], v[13], seed[2], seed[3]);
+    VB3_G(v[2], v[6], v[10], v[14], seed[4], seed[5]);
+    VB3_G(v[3], v[7], v[11], v[15], seed[6], seed[7]);
+    VB3_G(v[0], v[5], v[10], v[15], r0, r1);
+    VB3_G(v[2], v[7], v[8], v[13], z, z);
+    VB3_G(v[3], v[4], v[9], v[14], z, z);
+}
+__device__ __forceinline__ uint64_t pad_prg_from(const uint32_t* __restrict__ prefix, const uint32_t (&seed)[8],
+                                                 uint64_t row, uint64_t k) {
+    uint32_t v[16], m[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = prefix[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m[i] = seed[i];
+    m[8] = (uint32_t)row; m[9] = (uint32_t)(row >> 32);
+    m[10] = (uint32_t)k;  m[11] = (uint32_t)(k >> 32);
+    m[12] = m[13] = m[14] = m[15] = 0;
+    VB3_G(v[1], v[6], v[11], v[12], m[10], m[11]);
+    round_fn<1>(v, m); round_fn<2>(v, m); round_fn<3>(v, m);
+    round_fn<4>(v, m); round_fn<5>(v, m); round_fn<6>(v, m);
+    uint64_t raw = (uint64_t)(v[0] ^ v[8]) | ((uint64_t)(v[1] ^ v[9]) << 32);
+    return raw >= 0xFFFFFFFF00000001ull ? raw - 0xFFFFFFFF00000001ull : raw;
+}
+
 // (hi:lo) mod p, canonical (p = 2^64 - 2^32 + 1; same steps as vgl::reduce128)
 __device__ __forceinline__ uint64_t reduce128_p(uint64_t lo, uint64_t hi) {
     const uint64_t EPS = 0xFFFFFFFFull, PP = 0xFFFFFFFF00000001ull;

@@ -178,7 +178,7 @@ def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
             n_in, n_out = shapes[name]
             rho = _rand_int8_field((seq,), g, dev)
             tau = _rand_int8_field((n_out,), g, dev)
-            a = cp.gl_matvec(X[name].view(torch.int64).T.contiguous().view(torch.uint64), rho)      # X^T rho  (n_in)
+            a = cp.gl_matmul(rho.reshape(1, -1), X[name])[0]                                          # rho^T X  (n_in), X streamed once
             b = cp.gl_matvec(W[name], tau)                                                            # W tau    (n_in)
             width = 1 << (n_in - 1).bit_length()
             fa = torch.zeros(width, dtype=torch.int64, device=dev); fa[:n_in] = a.view(torch.int64)
