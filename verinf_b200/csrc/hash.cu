@@ -59,6 +59,27 @@ __global__ void __launch_bounds__(128) k_hash_stream(StreamArgs a) {
         int nb = rows_here == 0 ? 1 : (int)((rows_here + 7) / 8);
         uint32_t cv[8];
         vb3::set_iv(cv);
+#ifndef VI_HASH_NO_FAST
+        if (rows_here == CHUNK_ROWS) {
+            // whole chunk: 16 full blocks, no row guards, constant block length (4.52 -> 4.18 ms for the
+            // 4096 x 2^18 matrix against the guarded loop below)
+            const uint64_t* q = p + r0 * ld;
+#pragma unroll 1
+            for (int b = 0; b < 16; ++b) {
+                uint32_t m[16];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const uint64_t x = __ldg(q + r * ld);
+                    m[2 * r] = (uint32_t)x;
+                    m[2 * r + 1] = (uint32_t)(x >> 32);
+                }
+                q += 8 * ld;
+                const uint32_t flags = (b == 0 ? vb3::CHUNK_START : 0) |
+                                       (b == 15 ? (vb3::CHUNK_END | (single ? vb3::ROOT : 0)) : 0);
+                vb3::compress(cv, m, a.ctr_base + count, 64, flags);
+            }
+        } else
+#endif
         for (int b = 0; b < nb; ++b) {
             int64_t rb = rows_here - b * 8 < 8 ? rows_here - b * 8 : 8;
             uint32_t m[16];

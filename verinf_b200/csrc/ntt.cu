@@ -180,6 +180,9 @@ struct PassArgs {
 #ifndef VI_MID_MINB
 #define VI_MID_MINB 2
 #endif
+#ifndef VI_PASS0_MINB
+#define VI_PASS0_MINB 4      // MODE 0 passes (strided loads straight into registers; encode pass 1 at
+#endif                       // K = 2^16: 3/4/5/6/8 blocks -> 2.95 / 2.79 / 2.89 / 3.77 / 5.11 ms)
 // MODE 0: input contiguous along columns; 1: along the DFT index
 // tiles of DFT length 2^4..2^8 always run 256 threads (4096 elements / 16 per thread)
 __host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4 && logl <= 8) ? 256 : 512; }
@@ -187,7 +190,7 @@ __host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4
 // PAD: the loader evaluates the pad PRG (pad_mode 1); a separate instantiation so that the loaders
 // without a pad do not carry its registers and barrier
 template <int LOGL, bool INV, int MODE, bool PAD = false>
-__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? VI_PASS_MINB : 1) k_pass(PassArgs a) {
+__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? (MODE == 0 ? VI_PASS0_MINB : VI_PASS_MINB) : 1) k_pass(PassArgs a) {
     using SC = Sched<LOGL, false>;
     constexpr int L = 1 << LOGL, EPT = SC::EPT;
     extern __shared__ uint64_t sm[];
