@@ -187,9 +187,10 @@ struct PassArgs {
 // tiles of DFT length 2^4..2^8 always run 256 threads (4096 elements / 16 per thread)
 __host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4 && logl <= 8) ? 256 : 512; }
 
-// PAD: the loader evaluates the pad PRG (pad_mode 1); a separate instantiation so that the loaders
-// without a pad do not carry its registers and barrier
-template <int LOGL, bool INV, int MODE, bool PAD = false>
+// LD selects the loader of a MODE 0 pass at compile time, so that the plain loaders do not carry the
+// registers, code and barrier of the others: 0 = plain rows or message rows without pad, 1 = message
+// rows with the PRG pad, 2 = K-quant lift (pad decided at run time)
+template <int LOGL, bool INV, int MODE, int LD = 0>
 __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? (MODE == 0 ? VI_PASS0_MINB : VI_PASS_MINB) : 1) k_pass(PassArgs a) {
     using SC = Sched<LOGL, false>;
     constexpr int L = 1 << LOGL, EPT = SC::EPT;
@@ -204,7 +205,7 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     const uint32_t ncols32 = (uint32_t)a.ncols;
     uint64_t v[EPT];
     if constexpr (MODE == 0) {
-        if (a.src_kind == SRC_PLAIN) {
+        if (LD == 0 && a.src_kind == SRC_PLAIN) {
             const uint64_t* src = a.in + item * a.in_item + colg * (int64_t)a.in_col;
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
@@ -215,7 +216,8 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
             // pad PRG: the part of the first BLAKE3 round that does not depend on the slot is computed once
             // per CTA (one CTA = one row) into the tile buffer, which is free until the first stage exchange
             uint32_t* prg_prefix = reinterpret_cast<uint32_t*>(sm);
-            if constexpr (PAD) {
+            const bool pad = LD == 1 || (LD == 2 && a.pad_mode == 1);
+            if (pad) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
                     seed[i] = (uint32_t)__ldg(a.seed + 4 * i) | ((uint32_t)__ldg(a.seed + 4 * i + 1) << 8) |
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
                 uint64_t x = 0;
                 if (valid) {
                     if (slot < a.ell) {
-                        if (a.src_kind == SRC_MSG) x = src[slot];
+                        if constexpr (LD != 2) x = src[slot];
                         else {
                             int64_t f = (a.kq_first_row + item) * a.ell + slot;
                             if (f < a.kq_dout * a.kq_din) {
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
                                 }
                             }
                         }
-                    } else if (PAD) x = vb3::pad_prg_from(prg_prefix, seed, (uint64_t)(a.row_off + item), (uint64_t)(slot - a.ell));
+                    } else if (pad) x = vb3::pad_prg_from(prg_prefix, seed, (uint64_t)(a.row_off + item), (uint64_t)(slot - a.ell));
                 }
                 v[j] = x;
             }
@@ -628,10 +630,10 @@ int tile_threads(int logL, int logC) {
 }
 size_t tile_smem(int logL, int logC) { return (size_t)(1 << logL) * ((1 << logC) + 1) * 8; }
 
-template <int LOGL, bool INV, int MODE, bool PAD = false>
+template <int LOGL, bool INV, int MODE, int LD = 0>
 int launch_pass_t(const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
     size_t smem = tile_smem(LOGL, a.logC);
-    auto fn = k_pass<LOGL, INV, MODE, PAD>;
+    auto fn = k_pass<LOGL, INV, MODE, LD>;
     if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = items * a.tiles_per_item;
     if (grid <= 0) return VI_OK;
@@ -644,9 +646,17 @@ int launch_pass_t(const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
 template <bool INV, int MODE>
 int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
     if constexpr (INV && MODE == 0) {
+        if (a.src_kind == SRC_KQ) {     // encode pass 1 lifting K-quant weights
+            switch (logL) {
+#define VI_CASE(x) case x: return launch_pass_t<x, true, 0, 2>(a, items, st, tag);
+                VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
+                VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10) VI_CASE(11) VI_CASE(12)
+#undef VI_CASE
+            }
+        }
         if (a.pad_mode == 1) {          // encode pass 1 with the PRG pad
             switch (logL) {
-#define VI_CASE(x) case x: return launch_pass_t<x, true, 0, true>(a, items, st, tag);
+#define VI_CASE(x) case x: return launch_pass_t<x, true, 0, 1>(a, items, st, tag);
                 VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
                 VI_CASE(6) VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10) VI_CASE(11) VI_CASE(12)
 #undef VI_CASE
