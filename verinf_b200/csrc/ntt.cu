@@ -289,12 +289,18 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     run_stages<LOGL, INV, false, 0>(v, sm, CP, col, w, a.twL);
 
 #pragma unroll
+    // Every MODE 0 pass is the first step of a four-step transform: four-step factor, no scaling, strided
+    // store.  MODE 1 passes are last steps: no factor, n^-1 on inverse transforms, and a store through
+    // shared memory only for the single-pass transform (rows contiguous along the output index).
     for (int j = 0; j < EPT; ++j) {
         uint32_t k = SC::last_k(j, w);
-        if (a.fs && valid) v[j] = mul(v[j], __ldg(a.fs + col0 + (k * ncols32 + (uint32_t)col)));
-        if (a.scale != 1) v[j] = mul(v[j], a.scale);
+        if constexpr (MODE == 0) {
+            if (valid) v[j] = mul(v[j], __ldg(a.fs + col0 + (k * ncols32 + (uint32_t)col)));
+        } else if constexpr (INV) {
+            if (a.scale != 1) v[j] = mul(v[j], a.scale);
+        }
     }
-    if (!a.out_via_smem) {
+    if (MODE == 0 || !a.out_via_smem) {
         if (valid) {
             uint64_t* dst = a.out + item * a.out_item + colg * (int64_t)a.out_col;
 #pragma unroll
