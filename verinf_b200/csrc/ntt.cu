@@ -183,6 +183,9 @@ struct PassArgs {
 #ifndef VI_PASS0_MINB
 #define VI_PASS0_MINB 4      // MODE 0 passes (strided loads straight into registers; encode pass 1 at
 #endif                       // K = 2^16: 3/4/5/6/8 blocks -> 2.95 / 2.79 / 2.89 / 3.77 / 5.11 ms)
+// Columns per tile: fixed by the tile length from 128 points up (so that all tile index arithmetic is
+// compile-time), chosen by the host from the column count below that (tile_logC on the host).
+__host__ __device__ constexpr int fixed_logC(int logl) { return logl < 7 ? -1 : logl == 7 ? 5 : logl <= 9 ? 4 : 13 - logl; }
 // MODE 0: input contiguous along columns; 1: along the DFT index
 // tiles of DFT length 2^4..2^8 always run 256 threads (4096 elements / 16 per thread)
 __host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4 && logl <= 8) ? 256 : 512; }
@@ -195,8 +198,9 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     using SC = Sched<LOGL, false>;
     constexpr int L = 1 << LOGL, EPT = SC::EPT;
     extern __shared__ uint64_t sm[];
-    const int tid = threadIdx.x, C = 1 << a.logC, CP = C + 1;
-    const int col = tid & (C - 1), w = tid >> a.logC;
+    const int logC = fixed_logC(LOGL) >= 0 ? fixed_logC(LOGL) : a.logC;
+    const int tid = threadIdx.x, C = 1 << logC, CP = C + 1;
+    const int col = tid & (C - 1), w = tid >> logC;
     const int64_t item = blockIdx.x / a.tiles_per_item;
     const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
     const int64_t colg = col0 + col;
@@ -270,11 +274,16 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     } else {
         const int nthr = blockDim.x;
         const uint64_t* src = a.in + item * a.in_item + col0 * (int64_t)a.in_col;
-        if (LOGL >= 4 && a.logC == 4) {
+        if (LOGL >= 4 && logC == 4) {
             // 16 columns: the block has L threads, thread tid loads index tid of every column
             const uint64_t* p = src + (uint32_t)tid * a.in_idx;
+            if (ncols_tile == 16) {
 #pragma unroll
-            for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = cl < ncols_tile ? p[(uint32_t)cl * a.in_col] : 0;
+                for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = p[(uint32_t)cl * a.in_col];
+            } else {
+#pragma unroll
+                for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = cl < ncols_tile ? p[(uint32_t)cl * a.in_col] : 0;
+            }
         } else {
             for (int e = tid; e < L * C; e += nthr) {
                 int idx = e & (L - 1), cl = e >> LOGL;
@@ -424,8 +433,9 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     constexpr int LR = SI::NS ? SI::logr(SI::NS - 1) : 0;   // last inverse radix == first forward radix
     static_assert(RHO == 0 || (LOGL >= 4 && (RHO == 2 || RHO == 4)), "shift-twist form needs radix-16 first stages");
     extern __shared__ uint64_t sm[];
-    const int tid = threadIdx.x, C = 1 << a.logC, CP = C + 1;
-    const int col = tid & (C - 1), w = tid >> a.logC;
+    const int logC = fixed_logC(LOGL) >= 0 ? fixed_logC(LOGL) : a.logC;
+    const int tid = threadIdx.x, C = 1 << logC, CP = C + 1;
+    const int col = tid & (C - 1), w = tid >> logC;
     const int64_t item = blockIdx.x / a.tiles_per_item;
     const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
     const int64_t colg = col0 + col;
@@ -436,10 +446,15 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     {
         const int nthr = blockDim.x;
         const uint64_t* src = a.s1 + item * a.K + col0 * L;
-        if (LOGL >= 4 && a.logC == 4) {
+        if (LOGL >= 4 && logC == 4) {
             // 16 columns: the block has L threads, thread tid loads index tid of every column
+            if (ncols_tile == 16) {
 #pragma unroll
-            for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = cl < ncols_tile ? src[cl * L + tid] : 0;
+                for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = src[cl * L + tid];
+            } else {
+#pragma unroll
+                for (int cl = 0; cl < 16; ++cl) sm[tid * 17 + cl] = cl < ncols_tile ? src[cl * L + tid] : 0;
+            }
         } else {
             for (int e = tid; e < L * C; e += nthr) {
                 int idx = e & (L - 1), cl = e >> LOGL;
@@ -621,13 +636,13 @@ constexpr int SINGLE_LOGL = 10;   // transforms up to this length run as one pas
 
 // columns per tile for a DFT length 2^logL given ncols available
 int pick_logC(int logL, int64_t ncols) {
-    int logC = logL <= 8 ? 12 - logL : 13 - logL;      // 4096-element tiles, 8192 for long DFTs
+    if (fixed_logC(logL) >= 0) return fixed_logC(logL);   // the kernels assume it
+    int logC = 12 - logL;                              // 4096-element tiles
     int logTPC = logL >= 4 ? logL - 4 : 0;
     if (logC > 9 - logTPC) logC = 9 - logTPC;          // at most 512 threads
     int need = vi::ilog2(ncols);
     if (need < 4) need = 4;
     if (logC > need && logC > 4) logC = need;
-    if (logC < 1) logC = 1;
     return logC;
 }
 int tile_threads(int logL, int logC) {
