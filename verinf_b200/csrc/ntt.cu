@@ -201,8 +201,10 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     const int logC = fixed_logC(LOGL) >= 0 ? fixed_logC(LOGL) : a.logC;
     const int tid = threadIdx.x, C = 1 << logC, CP = C + 1;
     const int col = tid & (C - 1), w = tid >> logC;
-    const int64_t item = blockIdx.x / a.tiles_per_item;
-    const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
+    const uint32_t tpi = (uint32_t)a.tiles_per_item;          // the grid has fewer than 2^31 tiles: 32-bit division
+    const uint32_t item32 = blockIdx.x / tpi;
+    const int64_t item = item32;
+    const int64_t col0 = (int64_t)(blockIdx.x - item32 * tpi) * C;
     const int64_t colg = col0 + col;
     const bool valid = colg < a.ncols;
     const int ncols_tile = a.ncols - col0 < C ? (int)(a.ncols - col0) : C;   // valid columns of this tile
@@ -436,8 +438,10 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     const int logC = fixed_logC(LOGL) >= 0 ? fixed_logC(LOGL) : a.logC;
     const int tid = threadIdx.x, C = 1 << logC, CP = C + 1;
     const int col = tid & (C - 1), w = tid >> logC;
-    const int64_t item = blockIdx.x / a.tiles_per_item;
-    const int64_t col0 = (blockIdx.x % a.tiles_per_item) * C;
+    const uint32_t tpi = (uint32_t)a.tiles_per_item;          // the grid has fewer than 2^31 tiles: 32-bit division
+    const uint32_t item32 = blockIdx.x / tpi;
+    const int64_t item = item32;
+    const int64_t col0 = (int64_t)(blockIdx.x - item32 * tpi) * C;
     const int64_t colg = col0 + col;
     const bool valid = colg < a.n1;
     const int ncols_tile = a.n1 - col0 < C ? (int)(a.n1 - col0) : C;
