@@ -177,6 +177,9 @@ struct PassArgs {
 #ifndef VI_PASS_MINB
 #define VI_PASS_MINB 5
 #endif
+#ifndef VI_PASS_MINB_L8
+#define VI_PASS_MINB_L8 4    // MODE 1 passes of 256-point tiles (encode pass 3 at K = 2^16: 3/4/5/6 blocks ->
+#endif                       // 6.03 / 5.98 / 6.21 / 6.56 ms; 128-point tiles prefer 5)
 #ifndef VI_MID_MINB
 #define VI_MID_MINB 2
 #endif
@@ -194,7 +197,7 @@ __host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4
 // registers, code and barrier of the others: 0 = plain rows or message rows without pad, 1 = message
 // rows with the PRG pad, 2 = K-quant lift (pad decided at run time)
 template <int LOGL, bool INV, int MODE, int LD = 0>
-__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? (MODE == 0 ? VI_PASS0_MINB : VI_PASS_MINB) : 1) k_pass(PassArgs a) {
+__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? (MODE == 0 ? VI_PASS0_MINB : (LOGL == 8 ? VI_PASS_MINB_L8 : VI_PASS_MINB)) : 1) k_pass(PassArgs a) {
     using SC = Sched<LOGL, false>;
     constexpr int L = 1 << LOGL, EPT = SC::EPT;
     extern __shared__ uint64_t sm[];
