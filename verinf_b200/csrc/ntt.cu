@@ -446,8 +446,9 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     const int64_t item = item32;
     const int64_t col0 = (int64_t)(blockIdx.x - item32 * tpi) * C;
     const int64_t colg = col0 + col;
-    const bool valid = colg < a.n1;
-    const int ncols_tile = a.n1 - col0 < C ? (int)(a.n1 - col0) : C;
+    // From 128-point tiles up every tile is full: n1 >= L >= 128 > C columns, all powers of two.
+    const bool valid = fixed_logC(LOGL) >= 0 ? true : colg < a.n1;
+    const int ncols_tile = fixed_logC(LOGL) >= 0 ? C : (a.n1 - col0 < C ? (int)(a.n1 - col0) : C);
     const uint32_t n1 = (uint32_t)a.n1, rho = (uint32_t)a.rho;
 
     {
@@ -978,6 +979,7 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         mid.s1 = s1; mid.polys = polys ? polys + r0 * k : nullptr; mid.s2 = codes ? s2 : nullptr;
         mid.logC = pick_logC(log2, n1);
         mid.n1 = n1; mid.tiles_per_item = (n1 + (1 << mid.logC) - 1) >> mid.logC;
+        VI_REQUIRE(fixed_logC(log2) < 0 || n1 % (int64_t(1) << mid.logC) == 0, "encode: internal tile shape");
         mid.rho = (int)rho; mid.K = k; mid.fsK = fs_fwd; mid.twist = twist; mid.k_inv = inv_pow2(logk);
         mid.cscale = cscale; mid.twRL = twRL; mid.fsN = fsN;
         rc = get_tw(n2, &mid.twL);
