@@ -364,9 +364,11 @@ struct SegPlan { int seg_level; int64_t nseg, seg_rows, seg_state_words, state_b
 SegPlan seg_plan(int64_t m, int64_t ncols) {
     SegPlan p{-1, 0, 0, 0, 0, 0, 0};
     const int64_t chunks = (m + CHUNK_ROWS - 1) / CHUNK_ROWS;
-    const char* off = getenv("VERINF_HASH_SEGMENTS");
-    if ((off && off[0] == '0') || ncols <= 0 || ncols >= 131072 || chunks < 4) return p;
-    int64_t want = (262144 + ncols - 1) / ncols;            // segments that would fill the GPU
+    const char* off = getenv("VERINF_HASH_SEGMENTS");        // "0": never; n >= 2: always n segments (experiments)
+    const int64_t forced = off ? atoll(off) : -1;
+    if (forced == 0 || ncols <= 0 || chunks < 4) return p;
+    if (forced < 2 && ncols >= 131072) return p;
+    int64_t want = forced >= 2 ? forced : (262144 + ncols - 1) / ncols;   // segments that would fill the GPU
     if (want > 64) want = 64;
     int lvl = 0;
     while ((chunks >> (lvl + 1)) >= want) ++lvl;             // largest 2^lvl with chunks / 2^lvl >= want

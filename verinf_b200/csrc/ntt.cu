@@ -937,6 +937,10 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
     VI_REQUIRE(scratch != nullptr && scratch_bytes >= per_row,
                "encode: scratch of at least %lld bytes required (see vi_encode_scratch_bytes)", (long long)per_row);
     int64_t chunk = scratch_bytes / per_row;
+    // Whole waves: with tiles per row a multiple of 16 (K >= 2^12) a row count that is a multiple of 37 makes
+    // every grid of the three passes a multiple of 148 SMs x 4 resident CTAs, so no launch ends in a
+    // nearly empty wave.
+    if (chunk > 37 && chunk < m) chunk -= chunk % 37;
     const uint64_t *fs_inv, *fs_fwd = nullptr, *twist = nullptr;
     int rc = get_fs(k, n2, true, &fs_inv);        // inverse step 1: columns j2 (n2 of them), index k1
     if (rc) return rc;
