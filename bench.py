@@ -44,10 +44,11 @@ def parse():
     ap.add_argument("--sumcheck", action="store_true", help="also time the 2^24 degree-3 sumcheck")
     ap.add_argument("--extra", action="store_true",
                     help="also run the secondary workloads: fused K-quant lift+encode, 7B-layer commit+sumcheck")
-    ap.add_argument("--micro", choices=["matmul", "fold", "sumcheck"],
+    ap.add_argument("--micro", choices=["matmul", "fold", "sumcheck", "int_pipes"],
                     help="run only one secondary kernel (1024 x 2048 x 2048 matmul, the fold of 1024 row pairs "
                          "at K = 16384, or the 2^24 x 3 degree-3 sumcheck) and print its figures; the cases the ncu "
-                         "summaries use")
+                         "summaries use.  int_pipes builds bench_int_pipes.cu into build/int_pipes and runs it "
+                         "(integer issue rates and field-primitive throughputs)")
     return ap.parse_args()
 
 
@@ -348,7 +349,22 @@ def time_sumcheck(torch, dev):
     return {"ms": best * 1e3, "algorithmic_gbs": nbytes / best / 1e9}
 
 
+def build_int_pipes():
+    """Compiles the integer-pipe / field-primitive microbenchmark (bench_int_pipes.cu) for sm_100a."""
+    from verinf_b200.build import _nvcc
+    out = ROOT / "build" / "int_pipes"
+    src = ROOT / "bench_int_pipes.cu"
+    out.parent.mkdir(exist_ok=True)
+    if not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
+        env = {k_: v for k_, v in os.environ.items() if k_ not in ("CC", "CXX")}
+        subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+                               "--expt-relaxed-constexpr", "-I", str(ROOT), "-o", str(out), str(src)], env=env)
+    return out
+
+
 def run_micro(a):
+    if a.micro == "int_pipes":
+        sys.exit(subprocess.call([str(build_int_pipes())]))
     import torch
     from verinf_b200 import workloads
     dev = torch.device("cuda:0")

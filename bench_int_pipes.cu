@@ -3,15 +3,17 @@
 // The hot path is bound by integer issue rates that no vendor peak figure covers, so the
 // denominators are measured: register-resident kernels, 8 independent chains per thread, one
 // instruction kind (or one field primitive) per kernel, timed with CUDA events.  Under
-// `ncu --metrics smsp__inst_executed.sum,sm__inst_executed_pipe_alu.sum,sm__inst_executed_pipe_fma.sum`
-// the same binary gives instructions per primitive.
-// Build: python -m verinf_b200.build --microbench ; run: verinf_b200/microbench/int_pipes
+// `ncu --metrics smsp__inst_executed.sum,sm__inst_executed_pipe_alu.sum,sm__inst_executed_pipe_fma.sum
+// --clock-control none` the same binary gives instructions per primitive.
+// Build and run: python bench.py --micro int_pipes   (binary: build/int_pipes)
 #include <cstdint>
 #include <cstdio>
 #include <cuda_runtime.h>
 
-#include "../csrc/dft_reg.cuh"
-#include "../csrc/gl.cuh"
+#include "verinf_b200/csrc/dft_lanes.cuh"
+#include "verinf_b200/csrc/dft_reg.cuh"
+#include "verinf_b200/csrc/gl.cuh"
+#include "verinf_b200/csrc/gl_lanes.cuh"
 
 namespace {
 constexpr int ITERS = 1024, CHAINS = 8, GRID = 148 * 8, BLOCK = 256;
@@ -67,6 +69,36 @@ __global__ void __launch_bounds__(BLOCK) k_field(uint64_t* out, uint64_t seed) {
     out[blockIdx.x * BLOCK + threadIdx.x] = acc;
 }
 
+// lane form (gl_lanes.cuh): 16 values of four 32-bit lanes per thread
+template <int OP>
+__global__ void __launch_bounds__(BLOCK) k_lanes(uint64_t* out, uint64_t seed) {
+    using namespace vln;
+    Q v[16];
+    W3 w[4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = from_u64((seed * (threadIdx.x + 1 + i * 977) + i) % vgl::P);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = make_w3((seed * (threadIdx.x + 77 + i * 13)) % vgl::P);
+    for (int it = 0; it < ITERS / 4; ++it) {
+        if (OP == 0) {                       // radix-16 DFT, then renormalise by one multiply every 4th round
+            vdft::dif<4, 4, false>(v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = shl_bits<1>(v[i]);   // keeps the lanes bounded (counted below)
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (OP == 1) v[i] = mul(v[i], w[i & 3]);
+            if (OP == 2) v[i] = shl_bits<12>(v[i]);
+            if (OP == 3) v[i] = from_u64(to_u64(v[i]));
+            if (OP == 4) v[i] = shl_bits<1>(v[i]);
+        }
+    }
+    uint64_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc ^= to_u64(v[i]);
+    out[blockIdx.x * BLOCK + threadIdx.x] = acc;
+}
+
 
 // ---- self-check of the device field primitives against 128-bit integer arithmetic ----------
 template <int S> __device__ bool chk_pow2(uint64_t x) {
@@ -98,6 +130,31 @@ __global__ void k_selfcheck(unsigned long long* bad) {
     if (!(chk_pow2<1>(a) && chk_pow2<12>(a) && chk_pow2<24>(a) && chk_pow2<31>(a) && chk_pow2<32>(a) && chk_pow2<36>(a) &&
           chk_pow2<48>(a) && chk_pow2<60>(a) && chk_pow2<63>(a) && chk_pow2<64>(a) && chk_pow2<72>(a) && chk_pow2<84>(a) &&
           chk_pow2<95>(a))) f |= 32;
+    {   // lane form against the same 128-bit arithmetic
+        using namespace vln;
+        const Q qa = from_u64(a), qb = from_u64(b | (i & 4 ? 0xFFFFFFFF00000000ull : 0));   // any 64-bit input
+        const uint64_t bb = (b | (i & 4 ? 0xFFFFFFFF00000000ull : 0)) % P;
+        if (to_u64(qa) != a) f |= 64;
+        if (to_u64(add(qa, qb)) != (uint64_t)((A + bb) % P)) f |= 128;
+        if (to_u64(sub(qa, qb)) != (uint64_t)((A + P - bb) % P)) f |= 128;
+        const Q pr = mul(qb, make_w3(a));
+        if (to_u64(pr) != (uint64_t)((A * bb) % P)) f |= 256;
+        for (int k = 0; k < 4; ++k) if (pr.x[k] >= NORM || pr.x[k] <= -NORM) f |= 512;
+        // a radix-16 DFT of 16 values in both forms (lanes reach 16 * NORM), then a multiply from there
+        uint64_t v[16]; Q q[16];
+        for (int k = 0; k < 16; ++k) { v[k] = edge_or_rand(i * 16 + k, 5); q[k] = mul(from_u64(v[k]), make_w3(1)); }
+        vdft::dif<4, 4, false>(v); vdft::dif<4, 4, false>(q);
+        for (int k = 0; k < 16; ++k) {
+            if (to_u64(q[k]) != v[k]) f |= 1024;
+            if (to_u64(mul(q[k], make_w3(b))) != mul(v[k], b)) f |= 2048;
+        }
+        for (int k = 0; k < 16; ++k) { v[k] = edge_or_rand(i * 16 + k, 6); q[k] = mul(from_u64(v[k]), make_w3(1)); }
+        vdft::dif<4, 4, true>(v); vdft::dif<4, 4, true>(q);
+        for (int k = 0; k < 16; ++k) if (to_u64(q[k]) != v[k]) f |= 4096;
+        if (to_u64(shl_bits<12>(pr)) != mul_pow2<12>(to_u64(pr)) || to_u64(shl_bits<23>(pr)) != mul_pow2<23>(to_u64(pr)) ||
+            to_u64(vln::mul_pow2<39>(pr)) != vgl::mul_pow2<39>(to_u64(pr)) ||
+            to_u64(vln::mul_pow2<156>(pr)) != vgl::sub(0, vgl::mul_pow2<60>(to_u64(pr)))) f |= 8192;
+    }
     if (f) atomicOr(bad, (unsigned long long)f);
 }
 
@@ -120,7 +177,7 @@ int main() {
         unsigned long long* bad; cudaMalloc(&bad, 8); cudaMemset(bad, 0, 8);
         k_selfcheck<<<4096, 256>>>(bad);
         unsigned long long h = 0; cudaMemcpy(&h, bad, 8, cudaMemcpyDeviceToHost);
-        printf("self-check of add/sub/mul/reduce128/mul_pow2 vs 128-bit arithmetic: %s (flags %llu) %s\n",
+        printf("self-check of add/sub/mul/reduce128/mul_pow2 and the lane form vs 128-bit arithmetic: %s (flags %llu) %s\n",
                h ? "MISMATCH" : "ok", h, cudaGetErrorString(cudaGetLastError()));
         cudaFree(bad);
     }
@@ -148,6 +205,11 @@ int main() {
     fld("gl mul_pow2<12>", 16, time_ms([&] { k_field<4><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
     fld("gl mul_pow2<48>", 16, time_ms([&] { k_field<5><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
     fld("gl mul_pow2<72>", 16, time_ms([&] { k_field<6><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("lanes radix-16 DFT (+shl_bits<1>) element-stage", 64, time_ms([&] { k_lanes<0><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("lanes mul", 16, time_ms([&] { k_lanes<1><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("lanes shl_bits<12>", 16, time_ms([&] { k_lanes<2><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("lanes to_u64 + from_u64", 16, time_ms([&] { k_lanes<3><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
+    fld("lanes shl_bits<1>", 16, time_ms([&] { k_lanes<4><<<GRID, BLOCK>>>((uint64_t*)d, 12345); }));
     cudaFree(d);
     return 0;
 }

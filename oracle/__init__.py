@@ -56,12 +56,17 @@ def lib():
         L.or_commit_rows.argtypes = [p, i64, i64, i64, p]; L.or_commit_rows.restype = None
         L.or_hash_subtree.argtypes = [p, i64, i64, i64, p]; L.or_hash_subtree.restype = None
         L.or_hash_merge_subtrees.argtypes = [p, p, C.c_int, i64, p]; L.or_hash_merge_subtrees.restype = C.c_int
+        L.or_set_threads.argtypes = [C.c_int]; L.or_set_threads.restype = C.c_int
         _lib = L
     return _lib
 
 
-def set_threads(n: int) -> None:
-    os.environ["OMP_NUM_THREADS"] = str(n)
+def set_threads(n: int = 0) -> int:
+    """Sets the OpenMP thread count of the oracle's loops (n > 0) and returns the count in effect.
+    A launcher's OMP_NUM_THREADS (torchrun exports 1) is overridden, not inherited."""
+    if n > 0:
+        os.environ["OMP_NUM_THREADS"] = str(n)
+    return int(lib().or_set_threads(int(n)))
 
 
 def _ptr(a):

@@ -22,6 +22,9 @@
 #include <stdlib.h>
 #include <string.h>
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define GL_P 0xFFFFFFFF00000001ULL
 typedef unsigned __int128 u128;
@@ -612,4 +615,17 @@ int or_hash_merge_subtrees(const uint8_t* cvs, const int32_t* levels, int nblock
             for (int b = 0; b < 4; ++b) out[j * 32 + 4 * i + b] = (uint8_t)(st[0][i] >> (8 * b));
     }
     return 0;
+}
+
+/* Thread count of the OpenMP loops above: sets it when n > 0 (an OMP_NUM_THREADS value inherited  */
+/* from a launcher is read once, at load time, and would otherwise stick) and returns the count in */
+/* effect.                                                                                         */
+int or_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
 }

@@ -215,6 +215,41 @@ def sumcheck_vectors():
     np.savez_compressed(HERE / "sumcheck_vectors.npz", **out)
 
 
+def sumcheck_masked_vectors():
+    """Masked sumcheck (layergkr/sumcheck.py:192-224): prove_terms with a mask tape and a carried
+    mask mu0, pure-Python branch; the cases follow layergkr/tests/test_sumcheck.py:59-68."""
+    out = {}
+    r = random.Random(47)
+    cases = {
+        "m_deg2_n4": (16, [(1, [0, 1])], 2),
+        "m_deg3_n6": (64, [(1, [0, 1, 2])], 3),
+        "m_terms_n8": (256, [(5, [0, 1, 2]), (P - 3, [1, 3]), (7, [2])], 4),
+    }
+    for name, (size, terms_idx, ntab) in cases.items():
+        tabs = [[r.randrange(P) for _ in range(size)] for _ in range(ntab)]
+        n_rounds = size.bit_length() - 1
+        deg = max(len(idx) for _, idx in terms_idx)
+        coins = [r.randrange(P) for _ in range(n_rounds)]
+        tape_vals = [r.randrange(P) for _ in range(deg * n_rounds)]
+        mu0 = r.randrange(P)
+        terms = [(c, [tabs[i] for i in idx]) for c, idx in terms_idx]
+        pf = sumcheck.prove_terms(terms, lambda i: coins[i], tape=sumcheck.MaskTape(list(tape_vals)), mu0=mu0)
+        ok, why = sumcheck.verify_terms(pf, terms, lambda i: coins[i])
+        assert ok, why
+        bare = sumcheck.prove_terms(terms, lambda i: coins[i])
+        assert pf.claim == (bare.claim + mu0) % P and pf.round_polys[0] != bare.round_polys[0]
+        out[f"{name}_tables"] = u64(tabs)
+        out[f"{name}_coins"] = u64(coins)
+        out[f"{name}_tape"] = u64(tape_vals)
+        out[f"{name}_mu0"] = u64([mu0])
+        out[f"{name}_claim"] = u64([pf.claim])
+        out[f"{name}_final_mask"] = u64([pf.final_mask])
+        out[f"{name}_polys"] = u64([[y for _, y in rp] for rp in pf.round_polys])
+        out[f"{name}_terms"] = np.array(
+            [[c] + idx + [-1] * (4 - len(idx)) for c, idx in terms_idx], dtype=object).astype(str)
+    np.savez_compressed(HERE / "sumcheck_masked_vectors.npz", **out)
+
+
 def merkle_path_vectors():
     """Opening paths from rs.build_tree + rs.merkle_path (same convention as
     prover/core.merkle_path) for every leaf of trees with 1, 2, 5, 8 and 13 leaves; each path is
@@ -285,7 +320,8 @@ def fold_vectors():
 if __name__ == "__main__":
     if len(sys.argv) > 2:                                         # only the named fixtures
         for name in sys.argv[2:]:
-            {"merkle_paths": merkle_path_vectors, "fold": fold_vectors}[name]()
+            {"merkle_paths": merkle_path_vectors, "fold": fold_vectors,
+             "sumcheck_masked": sumcheck_masked_vectors}[name]()
         sys.exit(0)
     fold_vectors()
     merkle_path_vectors()
@@ -294,6 +330,7 @@ if __name__ == "__main__":
     hash_vectors()
     kquant_vectors()
     sumcheck_vectors()
+    sumcheck_masked_vectors()
     encode_vectors()
     config1()
     print("golden fixtures written to", HERE)

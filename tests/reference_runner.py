@@ -1,0 +1,193 @@
+"""Runs the reference's own call stacks in a fresh process, on one of two backends.
+
+    python tests/reference_runner.py --backend shim|shim+layergkr|reference --job JOB
+
+The staged reference tree (baseline/_ref, see baseline/stage_reference.py) is put on sys.path
+unmodified.  With `--backend shim` the modules `cuda_primitives` / `kquant_cuda` are this
+library's (verinf_b200.shim.install()); with `--backend reference` they are the reference's
+own, JIT-built from its CUDA headers by its own `load_inline` call.  Module names collide, so
+each backend needs its own process.  `shim+layergkr` additionally swaps this package's fused
+encode / commit / sumcheck routines into the reference's `layergkr.gpu` module
+(verinf_b200.shim.install_layergkr()).  The last stdout line is a JSON object.
+
+Jobs
+  tests:<module>   import a reference test module (prover/tests/test_cuda_primitives.py,
+                   prover/tests/test_persistent_weights.py, layergkr/tests/test_gpu.py) and call
+                   every test_* function, as the reference's run_tests.py does
+  commit_weights   core.commit_weights (prover/core.py:874-910) of a small seeded tape at the
+                   production geometry: root and a digest of every Merkle level
+  kernels          encode_messages + hash_columns_streamed + merkle_build_blake3 at
+                   ELL=8192, K=16384, N=65536 on 1024 seeded rows: digests of the outputs and
+                   CUDA-event times
+  sumcheck         layergkr sumcheck.prove_terms through gpu.prove_terms_gpu on seeded tables
+"""
+import argparse
+import hashlib
+import importlib
+import json
+import sys
+import time
+import traceback
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "baseline" / "_ref"
+P = (1 << 64) - (1 << 32) + 1
+
+
+def setup(backend: str) -> None:
+    if not (REF / "prover" / "core.py").exists():
+        raise SystemExit("baseline/_ref is not staged (python baseline/stage_reference.py)")
+    sys.path.insert(0, str(ROOT))
+    if backend.startswith("shim"):
+        from verinf_b200 import shim
+        shim.install()
+    # the reference's own entry points push prover/ to sys.path[0] themselves; repeat it for direct imports
+    sys.path.insert(0, str(REF))
+    sys.path.insert(0, str(REF / "prover"))
+    import torch  # noqa: F401
+    import _uint64_compat  # noqa: F401  (the reference imports it before any prover op, demo/demo_llama7b.py:74)
+    if backend == "shim+layergkr":
+        shim.install_layergkr()
+
+
+def backend_identity() -> dict:
+    import cuda_primitives as cp
+    return {"cuda_primitives_file": str(Path(cp.__file__).resolve().relative_to(ROOT))}
+
+
+def job_tests(modname: str) -> dict:
+    path = {"test_cuda_primitives": REF / "prover" / "tests",
+            "test_persistent_weights": REF / "prover" / "tests",
+            "test_gpu": REF / "layergkr" / "tests",
+            "test_sumcheck": REF / "layergkr" / "tests",
+            "test_rs": REF / "layergkr" / "tests"}[modname]
+    sys.path.insert(0, str(path))
+    mod = importlib.import_module(modname)
+    passed, failed = [], {}
+    for name in [n for n in dir(mod) if n.startswith("test_") and callable(getattr(mod, n))]:
+        t0 = time.time()
+        try:
+            getattr(mod, name)()
+            passed.append([name, round(time.time() - t0, 3)])
+        except Exception:  # noqa: BLE001  (report every failure, keep going)
+            failed[name] = traceback.format_exc()[-1500:]
+    return {"module": modname, "passed": passed, "failed": failed}
+
+
+def _sha(t) -> str:
+    import torch
+    if t.dtype == torch.uint64:
+        t = t.view(torch.int64)
+    return hashlib.sha256(t.contiguous().cpu().numpy().tobytes()).hexdigest()
+
+
+def job_commit_weights() -> dict:
+    import torch
+    import core
+    from tape import Tape
+    cfg = core.LigeroConfig(ELL=8192, K_DEG=16384, N_LIG=65536, T_QUERIES=4)
+    tape = Tape(cfg, lazy=True)
+    g = torch.Generator().manual_seed(20240607)
+    for name, n in (("W_a", 70000), ("W_b", 1200000), ("W_c", 3333)):
+        data = torch.randint(0, 1 << 20, (n,), dtype=torch.int64, generator=g).to(torch.uint64).cuda()
+        wt = tape.commit(name, data, (n,), persistent=True)
+        tape.add(wt, wt)
+    art, _, m_w = core.commit_weights(tape, cfg)
+    h = hashlib.sha256()
+    n_nodes = 0
+    for lvl in art.levels:
+        for node in lvl:
+            h.update(bytes(node))
+            n_nodes += 1
+    return {"m_w": int(m_w), "root": bytes(art.root).hex(), "levels": len(art.levels), "nodes": n_nodes,
+            "levels_sha256": h.hexdigest()}
+
+
+def job_kernels() -> dict:
+    import torch
+    import core
+    from cuda_primitives import hash_columns_streamed, merkle_build_blake3, ntt_forward_batched
+    cfg = core.LigeroConfig(ELL=8192, K_DEG=16384, N_LIG=65536, T_QUERIES=4)
+    m = 1024
+    g = torch.Generator(device="cuda").manual_seed(99)
+    msgs = torch.randint(0, 1 << 62, (m, cfg.ELL), generator=g, dtype=torch.int64, device="cuda").view(torch.uint64)
+    seed = torch.arange(32, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps=3):
+        best, out = None, None
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            out = fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+        return out, best
+
+    (polys, codes), enc_ms = timed(lambda: core.encode_messages(msgs, cfg, master_seed=seed, row_offset=5))
+    leaves, hash_ms = timed(lambda: hash_columns_streamed(codes))
+    (root, levels), merkle_ms = timed(lambda: merkle_build_blake3(leaves))
+    # a plain batched NTT at the codeword length, the reference's Bailey path
+    x = msgs[:64].repeat(1, 8).contiguous()
+    _, ntt_ms = timed(lambda: ntt_forward_batched(x))
+    return {"rows": m, "ELL": cfg.ELL, "K": cfg.K_DEG, "N": cfg.N_LIG,
+            "polys_sha256": _sha(polys), "codes_sha256": _sha(codes), "leaves_sha256": _sha(leaves),
+            "root": bytes(root.cpu().tolist()).hex(), "n_levels": len(levels),
+            "ntt64x65536_sha256": _sha(x),
+            "encode_ms": enc_ms, "hash_ms": hash_ms, "merkle_ms": merkle_ms, "ntt64x65536_x3_ms": ntt_ms}
+
+
+def job_sumcheck() -> dict:
+    """layergkr.sumcheck.prove_terms above its device threshold (size * factors >= 2^16 routes to
+    gpu.prove_terms_gpu, layergkr/sumcheck.py:170-181), bare and masked (`tape`, `mu0`)."""
+    import random
+    from layergkr import sumcheck
+    from layergkr.transcript import Transcript
+    r = random.Random(11)
+    logn = 15
+    n = 1 << logn
+    tabs = [[r.randrange(P) for _ in range(n)] for _ in range(3)]
+    tr = Transcript(b"runner/sumcheck")
+    tr.absorb("seed", (7).to_bytes(8, "little"))
+    coins = tr.coin("sc", logn)
+    terms = [(1, [tabs[0], tabs[1], tabs[2]]), (P - 5, [tabs[1], tabs[2]])]
+    assert sumcheck._sumcheck_gpu_ok(), "the reference's own GPU == CPU sumcheck gate failed on this backend"
+    t0 = time.time()
+    pf = sumcheck.prove_terms(terms, lambda i: coins[i])
+    dt = time.time() - t0
+    tape = sumcheck.MaskTape([r.randrange(P) for _ in range(3 * logn)])
+    pm = sumcheck.prove_terms(terms, lambda i: coins[i], tape=tape, mu0=123456789)
+    h = hashlib.sha256(repr((pf.claim, pf.round_polys, pf.challenges,
+                             pm.claim, pm.round_polys, pm.challenges, pm.final_mask)).encode()).hexdigest()
+    return {"n": n, "claim": int(pf.claim), "masked_claim": int(pm.claim), "transcript_sha256": h, "s": dt}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--backend", choices=["shim", "shim+layergkr", "reference"], required=True)
+    ap.add_argument("--job", required=True)
+    a = ap.parse_args()
+    setup(a.backend)
+    out = {"backend": a.backend, "job": a.job}
+    try:
+        out.update(backend_identity())
+        if a.job.startswith("tests:"):
+            out.update(job_tests(a.job.split(":", 1)[1]))
+        elif a.job == "commit_weights":
+            out.update(job_commit_weights())
+        elif a.job == "kernels":
+            out.update(job_kernels())
+        elif a.job == "sumcheck":
+            out.update(job_sumcheck())
+        else:
+            raise SystemExit(f"unknown job {a.job}")
+    except Exception:  # noqa: BLE001
+        out["error"] = traceback.format_exc()[-3000:]
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -94,6 +94,48 @@ class PySumcheck:
         return [f[0] for f in self.t]
 
 
+class TensorSumcheck(PySumcheck):
+    """PySumcheck behind the device-resident interface of layergkr_gpu.SumcheckProblem
+    (round_device / run_device / tables / complete_samples) on CPU tensors, including its
+    convention that g(1) is left 0 after the first round."""
+
+    def __init__(self, tables, terms):
+        super().__init__(tables, terms)
+        self._seen = False
+
+    @property
+    def tables(self):
+        return _u64(np.array(self.t, dtype=np.uint64))
+
+    def round_device(self, r):
+        ys = self.round(r)
+        if ys is None:
+            return None, False
+        skip = r is not None and self._seen
+        self._seen = True
+        if skip:
+            ys[1] = 0
+        return _u64(np.array(ys, dtype=np.uint64)), skip
+
+    def run_device(self, coins):
+        buf = np.zeros((len(coins), 8), dtype=np.uint64)
+        r = None
+        for i, c in enumerate(coins):
+            ys = self.round(r)
+            if i:
+                ys[1] = 0
+            buf[i, :len(ys)] = ys
+            r = c
+        if coins:
+            self.round(r)
+        return _u64(buf)
+
+    @staticmethod
+    def complete_samples(rows, coins, prev=None, prev_coin=None):
+        from verinf_b200.layergkr_gpu import SumcheckProblem
+        return SumcheckProblem.complete_samples(rows, coins, prev, prev_coin)
+
+
 def _worker(rank, world, port, total_rows, ell, k, n, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="2")
     torch.set_num_threads(1)
@@ -113,6 +155,12 @@ def _worker(rank, world, port, total_rows, ell, k, n, q):
         local = PySumcheck([row[rank::world] for row in tabs.tolist()], terms)
         claim, polys, chals = D.prove_terms_sharded(
             local, lambda t: PySumcheck(_np(t).tolist(), terms), lambda i: coins[i], 6, "cpu")
+        # the same proof through the device-resident interface: per-round callback, then queued coins
+        for kw in ({}, {"coins": coins}):
+            loc = TensorSumcheck([row[rank::world] for row in tabs.tolist()], terms)
+            c2, p2, ch2 = D.prove_terms_sharded(loc, lambda t: TensorSumcheck(_np(t).tolist(), terms),
+                                                lambda i: coins[i], 6, "cpu", **kw)
+            assert (c2, p2, ch2) == (claim, polys, chals), f"device-interface path {kw and 'queued'} differs"
         q.put((rank, bytes(root.tolist()), red, claim, [[y for _, y in rp] for rp in polys], chals))
     finally:
         dist.destroy_process_group()

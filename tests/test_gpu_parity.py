@@ -446,6 +446,38 @@ def test_sumcheck_golden(golden, name):
     assert claim2 == claim and polys2 == polys
 
 
+def _mask_fn(tape_vals):
+    """mask(deg, mu) -> ascending coefficients of h with h(0) + h(1) = mu, drawing deg tape values
+    (layergkr/sumcheck.py:73-92: MaskTape.take + mask_poly_coeffs)."""
+    pos = [0]
+    inv2 = pow(2, P - 2, P)
+
+    def mask(deg, mu):
+        u = tape_vals[pos[0]:pos[0] + deg]
+        assert len(u) == deg, "mask tape exhausted"
+        pos[0] += deg
+        return [((mu - sum(u)) % P) * inv2 % P] + [x % P for x in u]
+    return mask
+
+
+@pytest.mark.parametrize("name", ["m_deg2_n4", "m_deg3_n6", "m_terms_n8"])
+def test_sumcheck_masked_golden(golden, name):
+    """Masked prover (layergkr/sumcheck.py:192-224, layergkr/gpu.py:395-406): the mask touches the
+    scalar samples only; transcript, claim and carried mask equal the reference's CPython prover."""
+    from verinf_b200 import layergkr_gpu as lg
+    g = golden.sumcheck_masked_vectors
+    tabs = g[f"{name}_tables"]
+    coins = [int(c) for c in g[f"{name}_coins"]]
+    tape = [int(v) for v in g[f"{name}_tape"]]
+    mu0 = int(g[f"{name}_mu0"][0])
+    dts = [dev(t) for t in tabs]
+    terms = [(c, [dts[i] for i in idx]) for c, idx in _terms_from(g, name)]
+    claim, polys, chals, mu = lg.prove_terms_gpu(terms, lambda i: coins[i], P, _mask_fn(tape), mu0)
+    assert claim == int(g[f"{name}_claim"][0])
+    assert [[y for _, y in rp] for rp in polys] == [[int(v) for v in row] for row in g[f"{name}_polys"]]
+    assert chals == coins and mu == int(g[f"{name}_final_mask"][0])
+
+
 @pytest.mark.parametrize("logn,terms", [(12, [(1, [0, 1, 2])]), (16, [(1, [0, 1, 2])]), (13, [(3, [0, 1]), (P - 1, [2])]),
                                         (10, [(1, [0, 1, 2, 3])]), (15, [(1, [0, 0])]), (11, [(2, [1, 0, 2])])])
 def test_sumcheck_vs_oracle(logn, terms):

@@ -109,6 +109,32 @@ def test_sumcheck_vectors(golden, name):
     assert np.array_equal(samples[:, :want.shape[1]], want)
 
 
+@pytest.mark.parametrize("name", ["m_deg2_n4", "m_deg3_n6", "m_terms_n8"])
+def test_sumcheck_masked_vectors(golden, name):
+    """Oracle samples plus the scalar mask of layergkr/sumcheck.py:192-224 reproduce the
+    reference's masked transcript (the mask never touches the tables)."""
+    g = golden.sumcheck_masked_vectors
+    terms = []
+    for row in g[f"{name}_terms"]:
+        vals = [int(v) for v in row]
+        terms.append((vals[0], [v for v in vals[1:] if v >= 0]))
+    coins = [int(c) for c in g[f"{name}_coins"]]
+    tape = [int(v) for v in g[f"{name}_tape"]]
+    claim, samples, _ = oracle.sumcheck(g[f"{name}_tables"], terms, coins)
+    deg = max(len(f) for _, f in terms)
+    mu = int(g[f"{name}_mu0"][0])
+    assert (claim + mu) % oracle.P == int(g[f"{name}_claim"][0])
+    inv2 = pow(2, oracle.P - 2, oracle.P)
+    ev = lambda h, x: sum(c * pow(x, i, oracle.P) for i, c in enumerate(h)) % oracle.P
+    for rnd, r in enumerate(coins):
+        u = tape[rnd * deg:(rnd + 1) * deg]
+        h = [((mu - sum(u)) % oracle.P) * inv2 % oracle.P] + u
+        got = [(int(samples[rnd][x]) + ev(h, x)) % oracle.P for x in range(deg + 1)]
+        assert got == [int(v) for v in g[f"{name}_polys"][rnd]]
+        mu = ev(h, r)
+    assert mu == int(g[f"{name}_final_mask"][0])
+
+
 @pytest.mark.parametrize("n", [1, 2, 5, 8, 13])
 def test_merkle_path_vectors(golden, n):
     g = golden.merkle_path_vectors

@@ -56,20 +56,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return SO
 
 
-def build_microbench() -> Path:
-    """Integer-pipe / field-primitive microbenchmark binary (verinf_b200/microbench/int_pipes)."""
-    src = HERE / "microbench" / "int_pipes.cu"
-    out = HERE / "microbench" / "int_pipes"
-    env = dict(os.environ)
-    env.pop("CC", None)
-    env.pop("CXX", None)
-    subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
-                           "-std=c++17", "--expt-relaxed-constexpr", "-o", str(out), str(src)], env=env)
-    return out
-
-
 if __name__ == "__main__":
-    if "--microbench" in sys.argv:
-        print(build_microbench())
-    else:
-        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

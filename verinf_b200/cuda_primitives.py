@@ -596,11 +596,10 @@ def lookup_multiplicities_into(x, table, mult, label=""):
 
 # ---- compatibility with the reference's private module handle ----------------------------------
 class _Module:
-    """Stands in for the reference's JIT extension object (`_ensure_compiled()`), for code
-    that reaches for merkle_one_level or the stream-hash trio directly."""
-
-    _stream_pos: dict = {}       # state data_ptr -> rows hashed so far
-    _stream_digests: dict = {}   # state data_ptr -> digests written by the closing update
+    """Stands in for the reference's JIT extension object (`_ensure_compiled()`), for code that
+    reaches for merkle_one_level directly.  The reference's private stream-hash trio has no
+    counterpart: MerkleColumnAccumulator here drives vi_hash_stream_update itself, and no caller
+    outside the reference's own accumulator uses the trio."""
 
     @staticmethod
     def merkle_one_level(nodes_u32):
@@ -614,36 +613,6 @@ class _Module:
         with torch.cuda.device(nodes_u32.device):
             check(LIB.vi_merkle_level(ptr(nodes_u32), n, ptr(out), stream_ptr()))
         return out
-
-    # The stream trio keeps the chunk counter on the host (all columns advance together).
-    _STATE_LEVELS = 40
-
-    @classmethod
-    def hash_columns_stream_init(cls, n_cols):
-        st = torch.empty((int(n_cols), cls._STATE_LEVELS * 32), dtype=torch.uint8, device="cuda")
-        cls._stream_pos[st.data_ptr()] = 0
-        return st
-
-    @classmethod
-    def hash_columns_stream_update(cls, states, chunk, is_last_chunk, n_chunks_total):
-        _chk_u64(chunk, "chunk")
-        if chunk.dim() != 2 or chunk.size(0) > _BLAKE3_CHUNK_ROWS:
-            raise RuntimeError("chunk must fit within one BLAKE3 chunk (128 rows)")
-        done = cls._stream_pos[states.data_ptr()]
-        n = chunk.size(0)
-        n_cols = chunk.size(1)
-        total = done + n if is_last_chunk else int(n_chunks_total) * _BLAKE3_CHUNK_ROWS
-        dig = torch.empty((n_cols, 32), dtype=torch.uint8, device=chunk.device)
-        with torch.cuda.device(chunk.device):
-            check(LIB.vi_hash_stream_update(ptr(states), n_cols, total, done, ptr(chunk), n, ptr(dig), stream_ptr()))
-        cls._stream_pos[states.data_ptr()] = done + n
-        if is_last_chunk:
-            cls._stream_digests[states.data_ptr()] = dig
-
-    @classmethod
-    def hash_columns_stream_finalize(cls, states, n_cols, n_chunks_total):
-        cls._stream_pos.pop(states.data_ptr(), None)
-        return cls._stream_digests.pop(states.data_ptr())
 
 
 def _ensure_compiled():

@@ -107,11 +107,12 @@ def commit_rows_sharded(msg_local, total_rows: int, backend, group=None, row_off
     n_blocks = sum(len(p) for p in plan)
     if n_blocks < 2:                                          # a single sub-tree would need the root flag inside
         assert world == 1 or all(len(p) == 0 for i, p in enumerate(plan) if i != 0)
-        leaves = backend.hash_columns(codes) if rank == 0 or world == 1 else None
-        if world > 1:
-            box = [leaves]
-            dist.broadcast_object_list(box, src=0, group=group)
-            leaves = box[0]
+        if rank == 0 or world == 1:
+            leaves = backend.hash_columns(codes)
+        else:
+            leaves = torch.empty((codes.shape[1], 32), dtype=torch.uint8, device=codes.device)
+        if world > 1:           # src is a global rank: the first member of the group
+            dist.broadcast(leaves, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         root, levels = backend.merkle(leaves)
         return root, levels, codes
     mine = [backend.hash_subtree(codes[b0 - r0:b0 - r0 + cnt], b0 // CHUNK_ROWS, lvl) for b0, cnt, lvl in plan[rank]]
@@ -132,16 +133,36 @@ def commit_rows_sharded(msg_local, total_rows: int, backend, group=None, row_off
     return root, levels, codes
 
 
+def _limbs(t_u64: torch.Tensor) -> torch.Tensor:
+    """(...,) uint64 -> (..., 2) int64 of 32-bit limbs (lo, hi), on the tensor's device."""
+    x = t_u64.contiguous().view(torch.int64)
+    return torch.stack([x & 0xFFFFFFFF, (x >> 32) & 0xFFFFFFFF], dim=-1)
+
+
+def _from_limbs(rows) -> List[int]:
+    """[(sum of lo limbs, sum of hi limbs)] -> field elements"""
+    return [(int(lo) + (int(hi) << 32)) % P for lo, hi in rows]
+
+
+def allreduce_field_device(t_u64: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum over the ranks of a small tensor of field elements, entirely on the device: returns
+    (..., 2) int64 limb sums (exact integers; reduce with _from_limbs after one host copy).
+    Collectives have no mod-p sum, so each 64-bit value travels as two 32-bit limbs in int64
+    lanes; the integer sum of up to 2^31 ranks cannot overflow."""
+    limbs = _limbs(t_u64)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(limbs, op=dist.ReduceOp.SUM, group=group)
+    return limbs
+
+
 def allreduce_field(values: Sequence[int], device, group=None) -> List[int]:
-    """Exact sum mod p over the ranks of a few field elements.  Collectives have no mod-p sum, so
-    each 64-bit value travels as two 32-bit limbs in int64 lanes (the integer sum of up to 2^31
-    ranks cannot overflow) and is recombined and reduced on the host."""
+    """Exact sum mod p over the ranks of a few field elements held as Python ints."""
     vals = [int(v) % P for v in values]
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return vals
     limbs = torch.tensor([[v & 0xFFFFFFFF, v >> 32] for v in vals], dtype=torch.int64, device=device)
     dist.all_reduce(limbs, op=dist.ReduceOp.SUM, group=group)
-    return [(int(lo) + (int(hi) << 32)) % P for lo, hi in limbs.cpu().tolist()]
+    return _from_limbs(limbs.cpu().tolist())
 
 
 def shard_table(table: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -150,48 +171,106 @@ def shard_table(table: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return table.view(torch.int64)[..., rank::world].contiguous().view(table.dtype)
 
 
+def _gather_tail(finals_u64: torch.Tensor, world: int, group) -> torch.Tensor:
+    """(n_tables,) residual entries of this rank -> (n_tables, world) gathered tables, on the device."""
+    mine = finals_u64.contiguous().view(torch.int64)
+    if world == 1:
+        return mine.reshape(-1, 1).view(torch.uint64)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine, group=group)
+    return torch.stack(parts, dim=1).contiguous().view(torch.uint64)
+
+
 def prove_terms_sharded(local_problem, make_problem: Callable, coin: Callable[[int], int], n_rounds: int,
-                        device, group=None):
+                        device, group=None, coins: Sequence[int] = None):
     """Sumcheck over tables sharded with shard_table().
 
-    local_problem  this rank's shard: object with claim() -> int, round(r or None) -> samples or
-                   None, finals() -> [value per table] (verinf_b200.layergkr_gpu.SumcheckProblem)
+    local_problem  this rank's shard (verinf_b200.layergkr_gpu.SumcheckProblem, or any object
+                   with round(r or None) -> samples or None and finals() -> [value per table])
     make_problem   builds the same kind of object from an (n_tables, G) uint64 tensor of gathered
                    residual entries, for the last log2(G) rounds
+    coins          the challenges when they are known before the sumcheck starts (every call site
+                   of the reference pre-draws them, layergkr/full_layer.py:221-224): then nothing is
+                   read back per round -- the local rounds are queued, their partial samples are
+                   limb-split and all-reduced on the device in one collective, the residual entries
+                   all-gathered, the last log2(G) rounds queued, and one host copy ends the proof.
+                   Without `coins` the per-round callback `coin(i)` is honoured: one all-reduce
+                   (device limbs) and one small host read per round.
     Returns (claim, round_polys, challenges) identical to the unsharded prover's."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     log_g = world.bit_length() - 1
     assert 1 << log_g == world, "world size must be a power of two"
     local_rounds = n_rounds - log_g
     assert local_rounds >= 0, "tables smaller than the world size"
-    claim = allreduce_field([local_problem.claim()], device, group)[0]
+    on_device = hasattr(local_problem, "round_device")
+    if coins is not None and on_device:
+        return _prove_sharded_queued(local_problem, make_problem, [int(c) % P for c in coins], local_rounds,
+                                     n_rounds, world, group)
+    from .layergkr_gpu import _interp_at
     polys, chals = [], []
-    r = None
+    r, prev = None, None
     for rnd in range(local_rounds):
-        ys = allreduce_field(local_problem.round(r), device, group)
+        if on_device:
+            out, skipped = local_problem.round_device(r)
+            ys = _from_limbs(allreduce_field_device(out, group).cpu().tolist())     # one host read per round
+            if skipped:                                  # g(0) + g(1) = g_prev(r) holds for the global sums
+                ys[1] = (_interp_at(prev, r) - ys[0]) % P
+        else:
+            ys = allreduce_field(local_problem.round(r), device, group)
         polys.append(list(enumerate(ys)))
-        r = coin(rnd) % P
+        prev = ys
+        r = (coin(rnd) if coins is None else coins[rnd]) % P
         chals.append(r)
     if local_rounds:
-        local_problem.round(r)                    # last local fold: one residual entry per table
-    if log_g == 0:
-        return claim, polys, chals
-    mine = torch.tensor([[v & 0xFFFFFFFF, v >> 32] for v in local_problem.finals()], dtype=torch.int64, device=device)
-    parts = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(parts, mine, group=group)
-    rows = [[(int(lo) + (int(hi) << 32)) for lo, hi in p.cpu().tolist()] for p in parts]   # [rank][table]
-    n_tables = len(rows[0])
-    tail = torch.tensor([[_as_i64(rows[g][t]) for g in range(world)] for t in range(n_tables)],
-                        dtype=torch.int64, device=device).view(torch.uint64)
-    tail_problem = make_problem(tail)
-    r = None
-    for rnd in range(local_rounds, n_rounds):
-        ys = tail_problem.round(r)
-        polys.append(list(enumerate(ys)))
-        r = coin(rnd) % P
-        chals.append(r)
-    tail_problem.round(r)
+        local_problem.round_device(r) if on_device else local_problem.round(r)   # last local fold
+    if log_g:
+        if on_device:
+            tail = _gather_tail(local_problem.tables[:, 0], world, group)
+        else:
+            mine = torch.tensor([[v & 0xFFFFFFFF, v >> 32] for v in local_problem.finals()], dtype=torch.int64,
+                                device=device)
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine, group=group)
+            rows = [[(int(lo) + (int(hi) << 32)) for lo, hi in p.cpu().tolist()] for p in parts]   # [rank][table]
+            tail = torch.tensor([[_as_i64(rows[g][t]) for g in range(world)] for t in range(len(rows[0]))],
+                                dtype=torch.int64, device=device).view(torch.uint64)
+        tail_problem = make_problem(tail)
+        r = None
+        for rnd in range(local_rounds, n_rounds):
+            ys = tail_problem.round(r)
+            polys.append(list(enumerate(ys)))
+            r = (coin(rnd) if coins is None else coins[rnd]) % P
+            chals.append(r)
+        tail_problem.round(r)
+    claim = (polys[0][0][1] + polys[0][1][1]) % P if polys else \
+        allreduce_field([local_problem.claim()], device, group)[0]     # sum over the hypercube = g_0(0) + g_0(1)
     return claim, polys, chals
+
+
+def _prove_sharded_queued(local_problem, make_problem, coins, local_rounds, n_rounds, world, group):
+    """prove_terms_sharded with the challenges known up front; see there."""
+    deg = local_problem.deg
+    red = None
+    if local_rounds:
+        buf = local_problem.run_device(coins[:local_rounds])            # (local_rounds, 8), nothing read back
+        red = allreduce_field_device(buf[:, :deg + 1], group)           # (local_rounds, deg + 1, 2) limb sums
+    tail_buf = None
+    if n_rounds > local_rounds:
+        tail_problem = make_problem(_gather_tail(local_problem.tables[:, 0], world, group))
+        tail_buf = tail_problem.run_device(coins[local_rounds:])
+    rows = []
+    if red is not None:
+        rows += [_from_limbs(r) for r in red.cpu().tolist()]
+    n_local = len(rows)
+    if tail_buf is not None:
+        host = tail_buf.view(torch.int64).cpu().view(torch.uint64)
+        rows += [[int(v) for v in row[:deg + 1].tolist()] for row in host]
+    out = type(local_problem).complete_samples(rows[:n_local], coins[:n_local])
+    if tail_buf is not None:       # the first tail round is evaluated in full; later ones follow from their predecessor
+        out += type(local_problem).complete_samples(rows[n_local:], coins[n_local:])
+    polys = [list(enumerate(ys)) for ys in out]
+    claim = (out[0][0] + out[0][1]) % P
+    return claim, polys, list(coins[:n_rounds])
 
 
 def _as_i64(v: int) -> int:

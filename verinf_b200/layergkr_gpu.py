@@ -143,6 +143,7 @@ class SumcheckProblem:
         self._partials = scratch(LIB.vi_sumcheck_scratch_bytes(), dev, "sumcheck")
         self._host = torch.empty(8, dtype=torch.uint64).pin_memory()
         self._prev = None       # samples of the previous round (to derive g(1) of the next one)
+        self._seen_round = False
 
     def _args(self):
         return (self.tables.size(1), self.n_tables, self.size, self.n_terms,
@@ -159,18 +160,31 @@ class SumcheckProblem:
                                         stream_ptr()))
         return self._read(1)[0]
 
-    def round(self, r: Optional[int]) -> Optional[List[int]]:
-        """Fold with r (None on the first round), then return the samples g(0..deg) of the
-        current tables, or None once the tables are down to a single entry."""
+    def round_device(self, r: Optional[int]):
+        """Fold with r (None on the first round) and launch the evaluation of the next round without
+        reading anything back.  Returns (samples, skipped): `samples` is a device view of g(0..deg)
+        (valid until the next launch on this problem), or None once the tables are down to one entry;
+        with `skipped` True g(1) was not computed (written as 0) and follows from
+        g(0) + g(1) = g_prev(r).  For callers that combine the samples of several shards on the
+        device before any host read."""
         fold = r is not None
-        # after the first round g(1) is not computed on the device: g(0) + g(1) = g_prev(r)
-        skip = fold and self._prev is not None
+        skip = fold and self._seen_round
         with torch.cuda.device(self.tables.device):
             check(LIB.vi_sumcheck_round(ptr(self.tables), *self._args(), int(fold) | (2 if skip else 0),
                                         (r or 0) % P, ptr(self._out), ptr(self._partials), stream_ptr()))
         if fold:
             self.size //= 2
         if self.size < 2:
+            return None, False
+        self._seen_round = True
+        return self._out[:self.deg + 1], skip
+
+    def round(self, r: Optional[int]) -> Optional[List[int]]:
+        """Fold with r (None on the first round), then return the samples g(0..deg) of the
+        current tables, or None once the tables are down to a single entry."""
+        # after the first round g(1) is not computed on the device: g(0) + g(1) = g_prev(r)
+        out, skip = self.round_device(r)
+        if out is None:
             return None
         ys = self._read(self.deg + 1)
         if skip:
@@ -178,22 +192,43 @@ class SumcheckProblem:
         self._prev = ys
         return ys
 
+    def run_device(self, coins: Sequence[int]):
+        """All rounds queued back to back for challenges known up front; nothing is read back.
+        Returns the (n_rounds, 8) uint64 device buffer of samples: row i holds g_i(0..deg) with
+        g_i(1) left 0 for i >= 1 (see complete_samples)."""
+        n_rounds = self.size.bit_length() - 1
+        assert len(coins) == n_rounds
+        buf = torch.zeros((max(n_rounds, 1), 8), dtype=torch.uint64, device=self.tables.device)
+        if n_rounds:
+            cs = np.array([int(c) % P for c in coins], dtype=np.uint64)
+            with torch.cuda.device(self.tables.device):
+                check(LIB.vi_sumcheck_run(ptr(self.tables), *self._args(), cs.ctypes.data, n_rounds, ptr(buf),
+                                          ptr(self._partials), stream_ptr()))
+        self.size = 1
+        return buf[:n_rounds]
+
+    @staticmethod
+    def complete_samples(rows: List[List[int]], coins: Sequence[int], prev: Optional[List[int]] = None,
+                         prev_coin: Optional[int] = None) -> List[List[int]]:
+        """Fills the g(1) that the queued rounds leave out: g_i(1) = g_{i-1}(coins[i-1]) - g_i(0).
+        Row 0 is complete unless `prev` (the samples of the round before it) is given."""
+        out = [list(r) for r in rows]
+        for i in range(len(out)):
+            if i == 0 and prev is None:
+                continue
+            p_ys, p_r = (prev, prev_coin) if i == 0 else (out[i - 1], coins[i - 1])
+            out[i][1] = (_interp_at(p_ys, int(p_r) % P) - out[i][0]) % P
+        return out
+
     def run(self, coins: Sequence[int]):
         """All rounds back to back for challenges known up front (every call site of the reference
         pre-draws its coins from the transcript before the sumcheck starts): no host round trip per
         round, one D2H copy of all samples at the end.  Returns [[g(0..deg)] per round]."""
-        n_rounds = self.size.bit_length() - 1
-        assert len(coins) == n_rounds
-        buf = torch.empty((max(n_rounds, 1), 8), dtype=torch.uint64, device=self.tables.device)
-        cs = np.array([int(c) % P for c in coins], dtype=np.uint64)
-        with torch.cuda.device(self.tables.device):
-            check(LIB.vi_sumcheck_run(ptr(self.tables), *self._args(), cs.ctypes.data, n_rounds, ptr(buf),
-                                      ptr(self._partials), stream_ptr()))
-        self.size = 1
+        n_rounds = len(coins)
+        buf = self.run_device(coins)
         host = buf.view(torch.int64).cpu().view(torch.uint64)
-        out = [[int(v) for v in row[:self.deg + 1].tolist()] for row in host[:n_rounds]]
-        for i in range(1, n_rounds):      # g_i(1) = g_{i-1}(coins[i-1]) - g_i(0)
-            out[i][1] = (_interp_at(out[i - 1], int(cs[i - 1])) - out[i][0]) % P
+        rows = [[int(v) for v in row[:self.deg + 1].tolist()] for row in host[:n_rounds]]
+        out = self.complete_samples(rows, coins)
         self._prev = out[-1] if out else None
         return out
 

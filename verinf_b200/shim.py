@@ -20,3 +20,20 @@ def install() -> None:
     if pkg is not None:
         pkg.cuda_primitives = cuda_primitives
         pkg.kquant_cuda = kquant_cuda
+
+
+_LAYERGKR_FAST = ("encode_batch_ntt", "hash_and_tree", "prove_terms_gpu", "combine_t", "encode_batch_t",
+                  "gl_sum", "fold_t")
+
+
+def install_layergkr() -> None:
+    """Optional second step, after install() and with the reference's root on sys.path: replaces the
+    device routines of the reference's `layergkr.gpu` module (layergkr/gpu.py:141-410) by this
+    package's fused versions (one encode call, one fold+evaluate launch per sumcheck round).  The
+    module itself, its self-tests and every caller (`rs.py`, `sumcheck.py`, `layer.py`, ...) stay the
+    reference's: they look the routines up in `layergkr.gpu` by name."""
+    import importlib
+    from . import layergkr_gpu
+    gpu = importlib.import_module("layergkr.gpu")
+    for name in _LAYERGKR_FAST:
+        setattr(gpu, name, getattr(layergkr_gpu, name))
