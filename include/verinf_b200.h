@@ -105,8 +105,11 @@ int vi_hash_columns(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* dige
  * vi_hash_columns_noalloc_max_state_bytes() (= vi_hash_stream_state_bytes(ncols, m) for
  * m > 128; e.g. 65536 columns x up to 1024 rows) are rejected with an error.  The first
  * call on a device looks up the array's device address (cudaGetSymbolAddress); make that
- * first call before any stream capture.  All calls on a device share the array: calls
- * that overlap on the GPU race and must be serialised by the caller. */
+ * first call before any stream capture, and do not use the entry point on a device after a
+ * cudaDeviceReset (the looked-up address is kept).  All calls on a device share the array: calls
+ * that overlap on the GPU race and must be serialised by the caller.  Every input is hashed with
+ * one thread per column; vi_hash_columns splits matrices of fewer than 131072 columns into
+ * concurrent row segments, so narrow inputs take longer here (same digests). */
 int64_t vi_hash_columns_noalloc_max_state_bytes(void);
 int vi_hash_columns_noalloc(const uint64_t* mat, int64_t m, int64_t ncols, uint8_t* digests, void* stream);
 

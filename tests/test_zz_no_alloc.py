@@ -47,4 +47,4 @@ def test_noalloc_matches_regular_entry_point_twice():
     big = torch.zeros((2048, cols), dtype=torch.uint64, device="cuda")      # needs 5 levels x 2 MiB > 8 MiB
     out = torch.empty((cols, 32), dtype=torch.uint8, device="cuda")
     rc = lib.LIB.vi_hash_columns_noalloc(big.data_ptr(), 2048, cols, out.data_ptr(), lib.stream_ptr())
-    assert rc != 0 and b"built-in buffer" in lib.LIB.vi_last_error()
+    assert rc == 4 and b"built-in buffer" in lib.LIB.vi_last_error()      # VI_ERR_LIMIT

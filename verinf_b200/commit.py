@@ -155,6 +155,27 @@ class RowCommitter:
             main.synchronize()
         return bytes(self._root_host.tolist())
 
+    def copy_only(self, msg_host):
+        """The host-to-device part of commit_host alone: the same pinned rows, staging buffer, slices
+        and copy stream, no kernel.  What it takes is the floor the host memory and PCIe path set for
+        commit_host on this machine (used by the benchmark beside the end-to-end figure)."""
+        assert not msg_host.is_cuda and msg_host.is_pinned() and tuple(msg_host.shape) == (self.rows, self.ell)
+        with torch.cuda.device(self.device):
+            if self._stage is None:
+                self._stage = torch.empty((self.rows, self.ell), dtype=torch.uint64, device=self.device)
+                self._copy_stream = torch.cuda.Stream(device=self.device)
+            main = torch.cuda.current_stream()
+            step = (self.rows + self._slices - 1) // self._slices
+            if self.rows > 128 and step >= 128:
+                step = (step // 128) * 128
+            self._copy_stream.wait_stream(main)
+            with torch.cuda.stream(self._copy_stream):
+                for r0 in range(0, self.rows, step):
+                    cnt = min(step, self.rows - r0)
+                    self._stage[r0:r0 + cnt].copy_(msg_host[r0:r0 + cnt], non_blocking=True)
+            main.wait_stream(self._copy_stream)
+            main.synchronize()
+
     def open(self, cols):
         """Opening of the last commit at the queried columns: (columns (T, rows) uint64,
         siblings (T, depth, 32), sides (T, depth)), all on the device."""

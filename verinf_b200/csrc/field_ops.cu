@@ -1,11 +1,17 @@
 // Elementwise Goldilocks ops and the non-hot-path exports of the reference module
 // (poly_eval, dense/sparse mat-vec, lookup multiplicities, q_lin band interpreters).
 //
-// Replaces k_gl_mul/add/sub/pow (prover/cuda_primitives.py:208-223), k_neg /
-// k_axpy_inplace / k_poly_eval / k_lookup_multiplicities(_range)
-// (prover/kernels/gl_extras.cuh), k_matmul / k_matvec (prover/kernels/gl_matmul.cuh),
-// k_spmv / k_spmv_challenged (prover/kernels/gl_spmv.cuh) and the k_interp_band /
-// k_band_* kernels (prover/cuda_primitives.py:605-734).  All indexing is 64-bit.
+// Replaces k_gl_mul/add/sub/pow (prover/cuda_primitives.py:208-223), k_neg / k_axpy_inplace
+// (prover/kernels/gl_extras.cuh) and k_matmul / k_matvec (prover/kernels/gl_matmul.cuh); the
+// matmul, thin-matmul, matvec and product-column-sum kernels here are new (unreduced 160-bit
+// accumulation).
+//
+// Ported from the reference, not redesigned (none of them is on the hot path; they exist so that
+// every name the reference's callers import works): k_poly_eval and k_lookup follow
+// prover/kernels/gl_extras.cuh:93-149 with 64-bit indices, k_spmv merges the two kernels of
+// prover/kernels/gl_spmv.cuh:25-100, and k_band merges the five descriptor interpreters
+// k_interp_band / k_band_causal_id / k_band_causal_c2 / k_band_embed / k_band_rope_x of
+// prover/cuda_primitives.py:605-734 behind a `kind` switch, keeping their arithmetic and names.
 #include "../../include/verinf_b200.h"
 #include "blake3.cuh"
 #include "common.cuh"

@@ -59,7 +59,6 @@ __global__ void __launch_bounds__(128) k_hash_stream(StreamArgs a) {
         int nb = rows_here == 0 ? 1 : (int)((rows_here + 7) / 8);
         uint32_t cv[8];
         vb3::set_iv(cv);
-#ifndef VI_HASH_NO_FAST
         if (rows_here == CHUNK_ROWS) {
             // whole chunk: 16 full blocks, no row guards, constant block length (4.52 -> 4.18 ms for the
             // 4096 x 2^18 matrix against the guarded loop below)
@@ -79,7 +78,6 @@ __global__ void __launch_bounds__(128) k_hash_stream(StreamArgs a) {
                 vb3::compress(cv, m, a.ctr_base + count, 64, flags);
             }
         } else
-#endif
         for (int b = 0; b < nb; ++b) {
             int64_t rb = rows_here - b * 8 < 8 ? rows_here - b * 8 : 8;
             uint32_t m[16];
@@ -364,11 +362,10 @@ struct SegPlan { int seg_level; int64_t nseg, seg_rows, seg_state_words, state_b
 SegPlan seg_plan(int64_t m, int64_t ncols) {
     SegPlan p{-1, 0, 0, 0, 0, 0, 0};
     const int64_t chunks = (m + CHUNK_ROWS - 1) / CHUNK_ROWS;
-    const char* off = getenv("VERINF_HASH_SEGMENTS");        // "0": never; n >= 2: always n segments (experiments)
-    const int64_t forced = off ? atoll(off) : -1;
-    if (forced == 0 || ncols <= 0 || chunks < 4) return p;
-    if (forced < 2 && ncols >= 131072) return p;
-    int64_t want = forced >= 2 ? forced : (262144 + ncols - 1) / ncols;   // segments that would fill the GPU
+    // From 131072 columns up one thread per column fills the GPU (at 2^18 columns 8 segments made the hash
+    // kernel 6 % faster but the commit only 0.5 %, for 0.3 GB more scratch).
+    if (ncols <= 0 || chunks < 4 || ncols >= 131072) return p;
+    int64_t want = (262144 + ncols - 1) / ncols;                          // segments that would fill the GPU
     if (want > 64) want = 64;
     int lvl = 0;
     while ((chunks >> (lvl + 1)) >= want) ++lvl;             // largest 2^lvl with chunks / 2^lvl >= want
@@ -523,6 +520,13 @@ extern "C" int vi_challenge(const uint8_t* seed_dev, const uint8_t* label_dev, i
 // state is written before it is read within a call - but two calls that overlap on the
 // GPU (different streams, or different host threads) race on it and must be serialised
 // by the caller.
+//
+// The array's device address is looked up on the first call on each device and kept for the life
+// of the process: a cudaDeviceReset() on that device invalidates it, so a host that resets a device
+// must not call this entry point on it afterwards.  Every input takes the one-thread-per-column
+// path; vi_hash_columns cuts matrices with fewer than 131072 columns into concurrent row segments
+// (which needs more scratch than this array holds), so narrow inputs get the same digests here but
+// take longer than through vi_hash_columns.
 // ---------------------------------------------------------------------------
 namespace {
 constexpr int64_t NOALLOC_STATE_BYTES = int64_t(8) << 20;

@@ -551,6 +551,24 @@ struct DevTables {
 std::mutex g_mu;
 std::map<int, DevTables> g_tables;
 
+// Allocates a table and fills it from the host vector.  The copy is followed by a device-wide
+// synchronisation: a pageable-memory cudaMemcpy is ordered against the legacy default stream only
+// and may return before the DMA has finished, and the kernels that read the table run on the
+// caller's (possibly non-blocking) stream.  First use of a length must therefore happen outside
+// stream capture.  The buffer is freed again if the copy fails.
+int upload_table(const std::vector<uint64_t>& h, uint64_t** out) {
+    uint64_t* d = nullptr;
+    VI_CUDA(cudaMalloc(&d, h.size() * 8));
+    cudaError_t e = cudaMemcpy(d, h.data(), h.size() * 8, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return vi::fail(VI_ERR_CUDA, "twiddle table upload: %s", cudaGetErrorString(e));
+    }
+    *out = d;
+    return VI_OK;
+}
+
 int get_tw(int64_t n, const uint64_t** out) {
     int dev;
     VI_CUDA(cudaGetDevice(&dev));
@@ -562,8 +580,8 @@ int get_tw(int64_t n, const uint64_t** out) {
     uint64_t wn = vgl::hpow(7, (vgl::P - 1) / (uint64_t)n), cur = 1;
     for (int64_t e = 0; e < n; ++e) { h[(size_t)e] = cur; cur = vgl::hmul(cur, wn); }
     uint64_t* d = nullptr;
-    VI_CUDA(cudaMalloc(&d, (size_t)n * 8));
-    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
+    int rc_up = upload_table(h, &d);
+    if (rc_up) return rc_up;
     T.tw[n] = d;
     *out = d;
     return VI_OK;
@@ -590,8 +608,8 @@ int get_fs(int64_t n, int64_t ncols, bool inv, const uint64_t** out) {
         step = vgl::hmul(step, wn);
     }
     uint64_t* d = nullptr;
-    VI_CUDA(cudaMalloc(&d, (size_t)n * 8));
-    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
+    int rc_up = upload_table(h, &d);
+    if (rc_up) return rc_up;
     T.fs[key] = d;
     *out = d;
     return VI_OK;
@@ -613,8 +631,8 @@ int get_twist(int64_t K, int64_t N, const uint64_t** out) {
         for (int64_t l = 0; l < K; ++l) { h[(size_t)(t * K + l)] = cur; cur = vgl::hmul(cur, g); }
     }
     uint64_t* d = nullptr;
-    VI_CUDA(cudaMalloc(&d, (size_t)(rho * K) * 8));
-    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)(rho * K) * 8, cudaMemcpyHostToDevice));
+    int rc_up = upload_table(h, &d);
+    if (rc_up) return rc_up;
     T.twist[key] = d;
     *out = d;
     return VI_OK;
@@ -632,8 +650,8 @@ int get_cscale(int64_t K, const uint64_t** out) {
     uint64_t cur = vgl::hpow(vgl::hpow(2, (uint64_t)vi::ilog2(K)), vgl::P - 2);     // K^-1
     for (int64_t l = 0; l < K; ++l) { h[(size_t)l] = cur; cur = vgl::hmul(cur, 7); }
     uint64_t* d = nullptr;
-    VI_CUDA(cudaMalloc(&d, (size_t)K * 8));
-    VI_CUDA(cudaMemcpy(d, h.data(), (size_t)K * 8, cudaMemcpyHostToDevice));
+    int rc_up = upload_table(h, &d);
+    if (rc_up) return rc_up;
     T.cscale[K] = d;
     *out = d;
     return VI_OK;
@@ -722,10 +740,8 @@ int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
     return vi::check_launch("k_encode_mid");
 }
 // blow-up factors and tile lengths for which the shift-twist kernels are built
-// (VERINF_MID_SHIFT=0 selects the table-twist kernels everywhere, for comparison)
 bool mid_shift_form(int logL, int64_t rho) {
-    static const bool on = [] { const char* e = getenv("VERINF_MID_SHIFT"); return !(e && e[0] == '0'); }();
-    return on && (rho == 2 || rho == 4) && logL >= 4 && logL <= 10;
+    return (rho == 2 || rho == 4) && logL >= 4 && logL <= 10;
 }
 int launch_mid(int logL, const MidArgs& a, int64_t items, cudaStream_t st) {
     if (mid_shift_form(logL, a.rho)) {
@@ -753,15 +769,8 @@ uint64_t inv_pow2(int log) {   // 2^-log mod p
 // intermediates, ~15 rows) leave most SMs idle between the three dependent launches (57 ms per
 // commit); 1 GB chunks (~400 rows, thousands of CTAs per launch) give 37 ms although the
 // intermediates then round-trip through HBM, because every pass is integer-ALU bound, not
-// HBM bound.  VERINF_CHUNK_MB overrides the default for experiments.
-int64_t chunk_bytes() {
-    static const int64_t v = [] {
-        const char* e = getenv("VERINF_CHUNK_MB");
-        int64_t mb = e ? atoll(e) : 0;
-        return (mb > 0 ? mb : 1024) << 20;
-    }();
-    return v;
-}
+// HBM bound.  A caller that wants another chunk size passes a scratch buffer of that size.
+int64_t chunk_bytes() { return int64_t(1024) << 20; }
 
 }  // namespace
 

@@ -278,7 +278,10 @@ def gl_matmul(A, B, force_simt=False):
     m, k, n = A.size(0), A.size(1), B.size(1)
     Cm = torch.empty((m, n), dtype=_U64, device=A.device)
     with torch.cuda.device(A.device):
-        if m > 4 and n > 1 and m * k * n >= _TC_MIN_MACS and not force_simt:
+        # the tensor-core launch covers m < 65535 * 64 rows and k < 65535 * 32; beyond that (which the
+        # reference's kernel accepts) the scalar-pipe kernel takes any m and k < 2^32
+        tc_fits = (m + 63) // 64 <= 65535 and (k + 63) // 64 * 2 <= 65535
+        if m > 4 and n > 1 and m * k * n >= _TC_MIN_MACS and tc_fits and not force_simt:
             # large products: byte planes on the integer tensor cores (same result)
             nb = LIB.vi_gl_matmul_tc_scratch_bytes(m, k, n)
             sc = scratch(nb, A.device, "matmul")

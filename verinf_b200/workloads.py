@@ -53,9 +53,11 @@ def _timed(fn):
     return r, time.perf_counter() - t0
 
 
-def kquant_fused_encode(dev, qtype="Q4_K", seed=3):
+def kquant_fused_encode(dev, qtype="Q4_K", seed=3, check_rows=None):
     """Fused lift + encode workload: 11008x4096 weight as K-quant super-blocks -> lifted and RS-encoded
-    (transposed view, 5504 rows).  Compares the fused op with lift + transpose + pack + encode."""
+    (transposed view, 5504 rows).  Compares the fused op with lift + transpose + pack + encode.
+    With `check_rows` (row indices, negative = from the end) the result also carries, under "_check",
+    the raw super-blocks and those codeword rows on the host for an independent checker."""
     d_out, d_in = 11008, 4096
     nb = d_out * d_in // 256
     rng = np.random.default_rng(seed)
@@ -81,12 +83,21 @@ def kquant_fused_encode(dev, qtype="Q4_K", seed=3):
     a, b = unfused(), fused()
     same = bool(torch.equal(a.view(torch.int64), b.view(torch.int64)))
     rows = b.size(0)
+    chk = None
+    if check_rows is not None:
+        idx = sorted({int(i) % rows for i in check_rows})
+        sel = b.view(torch.int64)[torch.tensor(idx, device=dev)].cpu().numpy().view(np.uint64)
+        chk = {"raw": raw, "rows": idx, "codes": sel, "seed": bytes(range(32)), "S": S, "d_out": d_out, "d_in": d_in,
+               "ell": ELL, "k": K_DEG, "n": N_LIG}
     del a, b
     t_unf = _event_ms(unfused, reps=3, warm=1)
     t_fus = _event_ms(fused, reps=3, warm=1)
-    return {"qtype": qtype, "rows": rows, "bit_identical_to_unfused": same, "fused_ms": t_fus,
-            "unfused_ms": t_unf, "encoded_elems_per_s": rows * N_LIG / t_fus * 1e3,
-            "codeword_gbs": rows * N_LIG * 8 / t_fus / 1e6}
+    out = {"qtype": qtype, "rows": rows, "bit_identical_to_unfused": same, "fused_ms": t_fus,
+           "unfused_ms": t_unf, "encoded_elems_per_s": rows * N_LIG / t_fus * 1e3,
+           "codeword_gbs": rows * N_LIG * 8 / t_fus / 1e6}
+    if chk is not None:
+        out["_check"] = chk
+    return out
 
 
 def _event_ms(fn, reps=5, warm=2):
@@ -139,10 +150,14 @@ def fold_products(dev, rows=1024, k_deg=K_DEG, seed=9):
             "composed_ms": t_ref, "colsum_ms": t_sum, "colsum_gbs": 2 * rows * n_eval * 8 / t_sum / 1e6}
 
 
-def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
+def layer7b_commit_sumcheck(dev, seq=1000, seed=11, with_check=False):
     """Full-layer workload (dense row packing): int8 weights/activations of one Llama-2-7B-shaped layer,
     every weight and activation tensor committed (encode + column hash + Merkle), one deg-2
-    sumcheck per matmul on the projected vectors.  Returns stage seconds."""
+    sumcheck per matmul on the projected vectors, challenges drawn from a seeded transcript before
+    each sumcheck starts (layergkr/full_layer.py:221-224).  Returns stage seconds; with `with_check`
+    also, under "_check", what an independent checker needs to recompute the W_Q commitment and the
+    W_Q sumcheck transcript on the host."""
+    from .transcript import Transcript
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
     d, dff = 4096, 11008
@@ -172,8 +187,10 @@ def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
     commit_all()                                                  # warm-up (tables, allocator)
     (roots, n_rows), t_commit = _timed(commit_all)
 
-    def sumchecks():
+    def sumchecks(collect=None):
         ok = True
+        tr = Transcript(b"bench/layer7b")
+        tr.absorb("seed", int(seed).to_bytes(8, "little"))
         for name in shapes:
             n_in, n_out = shapes[name]
             rho = _rand_int8_field((seq,), g, dev)
@@ -183,19 +200,73 @@ def layer7b_commit_sumcheck(dev, seq=1000, seed=11):
             width = 1 << (n_in - 1).bit_length()
             fa = torch.zeros(width, dtype=torch.int64, device=dev); fa[:n_in] = a.view(torch.int64)
             fb = torch.zeros(width, dtype=torch.int64, device=dev); fb[:n_in] = b.view(torch.int64)
-            coins = [((i + 1) * 0x9E3779B97F4A7C15 + 7) % P for i in range(width.bit_length() - 1)]
             # the challenges of a layergkr sumcheck are drawn before it starts
             # (layergkr/full_layer.py:222 `coins = tr.coin(f"sc_{m.name}", n)`), so all rounds are queued at once
+            coins = tr.coin(f"sc_{name}", width.bit_length() - 1)
             claim, polys, _, _ = lg.prove_terms_gpu([(1, [fa.view(torch.uint64), fb.view(torch.uint64)])],
                                                     lambda i: coins[i], coins=coins)
             yt = cp.gl_matvec(Y[name], tau)                                                           # Y tau (seq)
             want = int(cp.gl_matvec(yt.reshape(1, -1), rho)[0].item())                                # rho^T Y tau
             ok = ok and claim == want and (polys[0][0][1] + polys[0][1][1]) % P == claim
+            if collect is not None and name == "W_Q":
+                to_np = lambda t: t.view(torch.int64).cpu().numpy().view(np.uint64)
+                collect.update(rho=to_np(rho), tau=to_np(tau), coins=list(coins), claim=int(claim),
+                               polys=[[int(y) for _, y in rp] for rp in polys])
         return ok
 
     sumchecks()
-    ok, t_sc = _timed(sumchecks)
-    return {"seq": seq, "rows_committed": n_rows, "codeword_gb": n_rows * N_LIG * 8 / 1e9,
-            "commit_s": t_commit, "sumcheck_s": t_sc, "commit_plus_sumcheck_s": t_commit + t_sc,
-            "witness_matmul_s": t_mm, "sumcheck_claims_match_rho_Y_tau": bool(ok),
-            "root_W_Q": roots["W_Q"].hex()}
+    chk = {} if with_check else None
+    ok, t_sc = _timed(lambda: sumchecks(chk))
+    out = {"seq": seq, "rows_committed": n_rows, "codeword_gb": n_rows * N_LIG * 8 / 1e9,
+           "commit_s": t_commit, "sumcheck_s": t_sc, "commit_plus_sumcheck_s": t_commit + t_sc,
+           "witness_matmul_s": t_mm, "sumcheck_claims_match_rho_Y_tau": bool(ok),
+           "root_W_Q": roots["W_Q"].hex()}
+    if with_check:
+        to_np = lambda t: t.view(torch.int64).cpu().numpy().view(np.uint64)
+        chk.update(W_Q=to_np(W["W_Q"]), X_Q=to_np(X["W_Q"]), seed=bytes(range(32)), root_W_Q=roots["W_Q"],
+                   ell=ELL, k=K_DEG, n=N_LIG)
+        out["_check"] = chk
+    return out
+
+
+def moe_expert_commits(dev, experts, d_ff=5120, d_model=8192, chunk_rows=1024, seed=17, prefix_check=False):
+    """MoE variant of the full layer (layergkr/full_layer.py:245-263): every expert weight
+    (d_ff x d_model int8, lifted with the signed-to-field map) gets its own commitment.  `experts` is the
+    list of expert indices this process commits (16 per GPU when 128 experts are split over 8 GPUs).
+    The 5120 message rows of an expert are generated and committed in chunks of `chunk_rows` through
+    StreamCommitter, so neither the lifted weight nor its codeword matrix is ever held.  Expert e's
+    data depends on (seed, e) only, so roots do not depend on how experts are split over processes.
+    Returns seconds, rows, and the roots; with `prefix_check` also the first chunk of the first expert
+    and the root of that chunk committed alone (for an independent checker)."""
+    from .commit import StreamCommitter
+    rows_per_expert = -(-(d_ff * d_model) // ELL)
+    seed_t = torch.arange(32, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev)
+
+    def expert_chunks(e):
+        g.manual_seed(seed * 1000003 + e)
+        left = d_ff * d_model
+        while left > 0:
+            n = min(left, chunk_rows * ELL)
+            flat = _signed_to_field(torch.randint(-128, 128, (n,), dtype=torch.int64, device=dev, generator=g))
+            yield _pack_rows(flat)
+            left -= n
+
+    def commit_expert(e):
+        sc = StreamCommitter(rows_per_expert, ELL, K_DEG, N_LIG, master_seed=seed_t, max_chunk_rows=chunk_rows,
+                             device=dev)
+        for chunk in expert_chunks(e):
+            sc.update(chunk.contiguous())
+        return bytes(sc.finalize().cpu().tolist())
+
+    if experts:
+        commit_expert(experts[0])                      # warm-up: tables, allocator
+    (roots, dt) = _timed(lambda: [commit_expert(e) for e in experts])
+    out = {"experts": list(experts), "rows": rows_per_expert * len(experts), "seconds": dt, "roots": roots,
+           "codeword_gb": rows_per_expert * len(experts) * N_LIG * 8 / 1e9}
+    if prefix_check and experts:
+        first = next(expert_chunks(experts[0])).contiguous()
+        root, _, _ = cp.commit_rows(first, K_DEG, N_LIG, master_seed=seed_t)
+        out["_check"] = {"msg": first.view(torch.int64).cpu().numpy().view(np.uint64), "seed": bytes(range(32)),
+                         "root": bytes(root.cpu().tolist()), "k": K_DEG, "n": N_LIG, "ell": ELL}
+    return out
