@@ -191,7 +191,7 @@ def cpu_self_check(a, torch, msg_dev, root_hex, k, n, payload):
     import numpy as np
     import oracle
     out = {}
-    crow = a.cpu_rows or auto_cpu_rows(a, budget_s=25.0)
+    crow = a.cpu_rows or auto_cpu_rows(a, budget_s=60.0)
     sample = msg_dev[:crow].view(torch.int64).cpu().numpy().view(np.uint64)
     base, _, root = cpu_commit(sample, n)
     if crow == a.rows:

@@ -87,6 +87,24 @@ __device__ __forceinline__ Q shl_bits(const Q& x) {
     return r;
 }
 
+// same value, lanes brought back below 2^24 + |x|_max / 2^24: carries move up one lane, the top
+// lane's carry re-enters lane 0 negated (psi^4 = -1).  For values that skip a multiply between two
+// butterfly stages.
+__device__ __forceinline__ Q renorm(const Q& x) {
+    int32_t l[4], h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        l[i] = x.x[i] & 0xFFFFFF;
+        h[i] = x.x[i] >> 24;
+    }
+    Q r;
+    r.x[0] = l[0] - h[3];
+    r.x[1] = l[1] + h[0];
+    r.x[2] = l[2] + h[1];
+    r.x[3] = l[3] + h[2];
+    return r;
+}
+
 // (a - b) * 2^E for a compile-time E in [0, 192): the sign (2^96 = -1) and the lane rotation
 // (psi^k) are folded into the subtraction, the remaining 2^r (r < 24) is one shl_bits.
 template <int E>

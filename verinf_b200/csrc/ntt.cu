@@ -29,6 +29,7 @@
 #include "dft_reg.cuh"
 #include "gl.cuh"
 #include "kquant.cuh"
+#include "ntt_lanes.cuh"
 
 namespace {
 
@@ -169,6 +170,10 @@ struct PassArgs {
     const void* kq_sT;       //   and the scales per (sub-block of k, n); null = decode from the super-blocks
     uint64_t kq_magic;       // floor(2^64 / kq_dout) + 1 when the matrix has fewer than 2^32 elements (then
                              // f / kq_dout = umul64hi(f, kq_magic) exactly), else 0: 64-bit division
+    // lane-form passes (k_pass_q): the same tables as balanced 24-bit digits, and the scale likewise
+    const vln::W3* twL3;
+    const vln::W3* fs3;
+    vln::W3 scale3;
 };
 
 // Minimum resident CTAs per SM asked of the compiler for the 256-thread tiles (register budget =
@@ -329,6 +334,110 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
         uint64_t* dst = a.out + item * a.out_item + col0 * (int64_t)a.out_col;
         for (int e = tid; e < L * C; e += nthr) {
             int k = e & (L - 1), cl = e >> LOGL;
+            if (cl < ncols_tile) dst[(uint32_t)cl * a.out_col + (uint32_t)k * a.out_k] = sm[k * CP + cl];
+        }
+    }
+}
+
+// Resident CTAs asked of the compiler for the lane-form passes (16-byte tile elements: 3 tiles of
+// 4096 elements fit in shared memory; 64 data registers per thread).
+#ifndef VI_PASSQ_MINB
+#define VI_PASSQ_MINB 2
+#endif
+
+// The tile pass of k_pass in lane form (gl_lanes.cuh), for the plain loaders (LD = 0): values are
+// converted from the canonical 64-bit form as they are loaded and back as they are stored; the
+// stages in between (butterflies, stage twiddles, four-step factor, n^-1) never leave lane form.
+template <int LOGL, bool INV, int MODE>
+__global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? VI_PASSQ_MINB : 1) k_pass_q(PassArgs a) {
+    using SC = Sched<LOGL, false>;
+    using vln::Q;
+    constexpr int L = 1 << LOGL, EPT = SC::EPT;
+    extern __shared__ int4 smq[];
+    const int logC = fixed_logC(LOGL) >= 0 ? fixed_logC(LOGL) : a.logC;
+    const int tid = threadIdx.x, C = 1 << logC, CP = C + 1;
+    const int col = tid & (C - 1), w = tid >> logC;
+    const uint32_t tpi = (uint32_t)a.tiles_per_item;
+    const uint32_t item32 = blockIdx.x / tpi;
+    const int64_t item = item32;
+    const int64_t col0 = (int64_t)(blockIdx.x - item32 * tpi) * C;
+    const int64_t colg = col0 + col;
+    const bool valid = colg < a.ncols;
+    const int ncols_tile = a.ncols - col0 < C ? (int)(a.ncols - col0) : C;
+    const uint32_t ncols32 = (uint32_t)a.ncols;
+    Q v[EPT];
+    if constexpr (MODE == 0) {
+        if (a.src_kind == SRC_PLAIN) {
+            const uint64_t* src = a.in + item * a.in_item + colg * (int64_t)a.in_col;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                v[j] = vln::from_u64(valid ? src[(uint32_t)SC::first_pos(j, w) * a.in_idx] : 0);
+        } else {       // message rows, zero past ELL
+            const uint64_t* src = a.in + item * a.ell;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                const int64_t slot = (int64_t)SC::first_pos(j, w) * a.in_idx + colg;
+                v[j] = vln::from_u64((valid && slot < a.ell) ? src[slot] : 0);
+            }
+        }
+    } else {
+        const int nthr = blockDim.x;
+        const uint64_t* src = a.in + item * a.in_item + col0 * (int64_t)a.in_col;
+        if (LOGL >= 4 && logC == 4) {
+            // 16 columns: the block has L threads, thread tid loads index tid of every column
+            const uint64_t* p = src + (uint32_t)tid * a.in_idx;
+            if (ncols_tile == 16) {
+#pragma unroll
+                for (int cl = 0; cl < 16; ++cl) vlt::sts_q(smq, tid * 17 + cl, vln::from_u64(p[(uint32_t)cl * a.in_col]));
+            } else {
+#pragma unroll
+                for (int cl = 0; cl < 16; ++cl)
+                    vlt::sts_q(smq, tid * 17 + cl, vln::from_u64(cl < ncols_tile ? p[(uint32_t)cl * a.in_col] : 0));
+            }
+        } else {
+            for (int e = tid; e < L * C; e += nthr) {
+                const int idx = e & (L - 1), cl = e >> LOGL;
+                vlt::sts_q(smq, idx * CP + cl,
+                           vln::from_u64(cl < ncols_tile ? src[(uint32_t)cl * a.in_col + (uint32_t)idx * a.in_idx] : 0));
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) v[j] = vlt::lds_q(smq, SC::first_pos(j, w) * CP + col);
+    }
+
+    vlt::run_stages_q<SC, LOGL, INV, 0>(v, smq, CP, col, w, a.twL3);
+
+    uint64_t o[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const uint32_t k = SC::last_k(j, w);
+        if constexpr (MODE == 0) {
+            // first step of a four-step transform: four-step factor (also for invalid columns: any entry)
+            const vln::W3 f = vlt::ldg_w3(a.fs3 + (valid ? col0 + (k * ncols32 + (uint32_t)col) : 0));
+            o[j] = vln::to_u64(vln::mul(v[j], f));
+        } else if constexpr (INV) {
+            o[j] = vln::to_u64(vln::mul(v[j], a.scale3));      // n^-1
+        } else {
+            o[j] = vln::to_u64(v[j]);
+        }
+    }
+    if (MODE == 0 || !a.out_via_smem) {
+        if (valid) {
+            uint64_t* dst = a.out + item * a.out_item + colg * (int64_t)a.out_col;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) dst[(uint32_t)SC::last_k(j, w) * a.out_k] = o[j];
+        }
+    } else {
+        uint64_t* sm = reinterpret_cast<uint64_t*>(smq);
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) sm[SC::last_k(j, w) * CP + col] = o[j];
+        __syncthreads();
+        const int nthr = blockDim.x;
+        uint64_t* dst = a.out + item * a.out_item + col0 * (int64_t)a.out_col;
+        for (int e = tid; e < L * C; e += nthr) {
+            const int k = e & (L - 1), cl = e >> LOGL;
             if (cl < ncols_tile) dst[(uint32_t)cl * a.out_col + (uint32_t)k * a.out_k] = sm[k * CP + cl];
         }
     }
@@ -547,6 +656,7 @@ struct DevTables {
     std::map<std::pair<int64_t, int64_t>, uint64_t*> twist;   // (K, N) -> (rho, K)
     std::map<int64_t, uint64_t*> cscale;                      // K -> K^-1 * 7^l
     std::map<std::tuple<int64_t, int64_t, bool>, uint64_t*> fs;   // (n, ncols, inverse) -> four-step factors
+    std::map<const uint64_t*, vln::W3*> w3;                   // table -> the same constants as balanced 24-bit digits
 };
 std::mutex g_mu;
 std::map<int, DevTables> g_tables;
@@ -569,6 +679,31 @@ int upload_table(const std::vector<uint64_t>& h, uint64_t** out) {
     return VI_OK;
 }
 
+// The lane-form kernels read their constants as three balanced 24-bit digits (vln::W3, 16 bytes).
+int upload_w3(const std::vector<uint64_t>& h, vln::W3** out) {
+    std::vector<vln::W3> hw(h.size());
+    for (size_t i = 0; i < h.size(); ++i) hw[i] = vln::make_w3(h[i]);
+    vln::W3* d = nullptr;
+    VI_CUDA(cudaMalloc(&d, hw.size() * sizeof(vln::W3)));
+    cudaError_t e = cudaMemcpy(d, hw.data(), hw.size() * sizeof(vln::W3), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return vi::fail(VI_ERR_CUDA, "twiddle table upload: %s", cudaGetErrorString(e));
+    }
+    *out = d;
+    return VI_OK;
+}
+// digits table of a u64 table returned by get_tw / get_fs (null if there is none)
+const vln::W3* w3_of(const uint64_t* table) {
+    int dev;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto& T = g_tables[dev];
+    auto it = T.w3.find(table);
+    return it == T.w3.end() ? nullptr : it->second;
+}
+
 int get_tw(int64_t n, const uint64_t** out) {
     int dev;
     VI_CUDA(cudaGetDevice(&dev));
@@ -582,7 +717,11 @@ int get_tw(int64_t n, const uint64_t** out) {
     uint64_t* d = nullptr;
     int rc_up = upload_table(h, &d);
     if (rc_up) return rc_up;
+    vln::W3* d3 = nullptr;
+    rc_up = upload_w3(h, &d3);
+    if (rc_up) { cudaFree(d); return rc_up; }
     T.tw[n] = d;
+    T.w3[d] = d3;
     *out = d;
     return VI_OK;
 }
@@ -610,7 +749,11 @@ int get_fs(int64_t n, int64_t ncols, bool inv, const uint64_t** out) {
     uint64_t* d = nullptr;
     int rc_up = upload_table(h, &d);
     if (rc_up) return rc_up;
+    vln::W3* d3 = nullptr;
+    rc_up = upload_w3(h, &d3);
+    if (rc_up) { cudaFree(d); return rc_up; }
     T.fs[key] = d;
+    T.w3[d] = d3;
     *out = d;
     return VI_OK;
 }
@@ -677,8 +820,30 @@ int tile_threads(int logL, int logC) {
 }
 size_t tile_smem(int logL, int logC) { return (size_t)(1 << logL) * ((1 << logC) + 1) * 8; }
 
+// Lane-form passes are used for the plain loaders of tile lengths 2^4 .. 2^10 (VI_LANES=0 builds the
+// library without them).
+#ifndef VI_LANES
+#define VI_LANES 1
+#endif
+template <int LOGL, bool INV, int MODE>
+int launch_pass_q(const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
+    size_t smem = 2 * tile_smem(LOGL, a.logC);
+    auto fn = k_pass_q<LOGL, INV, MODE>;
+    if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid = items * a.tiles_per_item;
+    if (grid <= 0) return VI_OK;
+    if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "tile grid too large (%lld)", (long long)grid);
+    vi::ProfScope prof(tag, st);
+    fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
+    return vi::check_launch("k_pass_q");
+}
+
 template <int LOGL, bool INV, int MODE, int LD = 0>
 int launch_pass_t(const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
+    if constexpr (VI_LANES && LD == 0 && LOGL >= 4 && LOGL <= 10) {
+        if (a.twL3 != nullptr && (MODE == 1 || a.fs3 != nullptr) && (a.src_kind == SRC_PLAIN || a.src_kind == SRC_MSG))
+            return launch_pass_q<LOGL, INV, MODE>(a, items, st, tag);
+    }
     size_t smem = tile_smem(LOGL, a.logC);
     auto fn = k_pass<LOGL, INV, MODE, LD>;
     if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -723,6 +888,9 @@ int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaSt
     a.tiles_per_item = (a.ncols + (1 << a.logC) - 1) >> a.logC;
     int rc = get_tw(int64_t(1) << logL, &a.twL);
     if (rc) return rc;
+    a.twL3 = w3_of(a.twL);
+    a.fs3 = a.fs ? w3_of(a.fs) : nullptr;
+    a.scale3 = vln::make_w3(a.scale);
     if (inv) return mode ? launch_pass_l<true, 1>(logL, a, items, st, tag) : launch_pass_l<true, 0>(logL, a, items, st, tag);
     return mode ? launch_pass_l<false, 1>(logL, a, items, st, tag) : launch_pass_l<false, 0>(logL, a, items, st, tag);
 }
@@ -787,6 +955,7 @@ extern "C" int vi_release_tables(void) {
         for (auto& t : kv.second.twist) cudaFree(t.second);
         for (auto& t : kv.second.fs) cudaFree(t.second);
         for (auto& t : kv.second.cscale) cudaFree(t.second);
+        for (auto& t : kv.second.w3) cudaFree(t.second);
     }
     g_tables.clear();
     VI_CUDA(cudaSetDevice(cur));
