@@ -489,6 +489,7 @@ def run_native(a):
         from verinf_b200 import workloads
         extra["field_matmul"] = workloads.field_matmul(dev)
         extra["fold_products"] = workloads.fold_products(dev)
+        extra["reference_cuda"] = reference_cuda_leg()
     if a.extra:
         # MoE variant: 128 experts x (5120 x 8192) int8, 16 per GPU at 8 GPUs, one commitment per expert,
         # roots gathered; with fewer ranks every rank still commits 16 experts (rank r: 16r .. 16r+15)
@@ -595,6 +596,35 @@ def run_native(a):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def reference_cuda_leg():
+    """The reference's own CUDA kernels beside this library on the same GPU (second, independent
+    witness and same-box number): tests/reference_runner.py runs `encode_messages`,
+    `hash_columns_streamed`, `merkle_build_blake3` and a batched NTT at the geometry the reference's
+    authors validated (ELL=8192, K=16384, N=65536, 1024 rows) once on the reference's JIT-built
+    extension and once on this library, from the staged tree baseline/_ref; digests must agree."""
+    runner = ROOT / "tests" / "reference_runner.py"
+    if not (ROOT / "baseline" / "_ref" / "prover" / "core.py").exists():
+        return {"unavailable": "baseline/_ref not staged (python baseline/stage_reference.py)"}
+    env = dict(os.environ)
+    env.setdefault("TORCH_EXTENSIONS_DIR", str(ROOT / "build" / "torch_extensions"))
+    res = {}
+    for backend in ("reference", "shim"):
+        p = subprocess.run([sys.executable, str(runner), "--backend", backend, "--job", "kernels"], capture_output=True,
+                           text=True, timeout=1500, env=env, cwd=str(ROOT))
+        lines = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
+        res[backend] = json.loads(lines[-1]) if lines else {"error": p.stderr[-500:]}
+        if "error" in res[backend]:
+            return {"unavailable": f"{backend} run failed: " + res[backend]["error"][-300:]}
+    ref, ours = res["reference"], res["shim"]
+    keys = ("polys_sha256", "codes_sha256", "leaves_sha256", "root", "ntt64x65536_sha256")
+    return {"geometry": {"rows": ref["rows"], "ELL": ref["ELL"], "K": ref["K"], "N": ref["N"]},
+            "bit_identical": all(ref[k_] == ours[k_] for k_ in keys),
+            "encode_ms": ref["encode_ms"], "hash_ms": ref["hash_ms"], "merkle_ms": ref["merkle_ms"],
+            "ntt_64x65536_ms": ref["ntt64x65536_x3_ms"],
+            "ours_encode_ms": ours["encode_ms"], "ours_hash_ms": ours["hash_ms"], "ours_merkle_ms": ours["merkle_ms"],
+            "ours_ntt_64x65536_ms": ours["ntt64x65536_x3_ms"]}
 
 
 def time_sumcheck(torch, dev):

@@ -33,6 +33,13 @@ __global__ void __launch_bounds__(BLOCK) k_raw(uint32_t* out, uint32_t a0, uint3
             if (OP == 3) asm volatile("shf.r.wrap.b32 %0, %0, %0, %1;" : "+r"(x[i]) : "r"(m));
             if (OP == 4) asm volatile("prmt.b32 %0, %0, %0, 0x1032;" : "+r"(x[i]));
             if (OP == 5) asm volatile("add.cc.u32 %0, %0, %2; addc.u32 %1, %1, %3;" : "+r"(x[i]), "+r"(y[i]) : "r"(m), "r"(a0));
+            if (OP == 7) asm volatile("mad.wide.s32 %0, %1, %2, %0;" : "+l"(z[i]) : "r"(x[i]), "r"(m));
+            if (OP == 8) {      // wide product, then a 64-bit add of an independent value (no fused accumulate)
+                uint64_t t;
+                asm volatile("mul.wide.s32 %0, %1, %2;" : "=l"(t) : "r"(x[i]), "r"(m));
+                asm volatile("add.s64 %0, %0, %1;" : "+l"(z[i]) : "l"(t));
+            }
+            if (OP == 9) asm volatile("mad.lo.s32 %0, %1, %2, %0;" : "+r"(y[i]) : "r"(x[i]), "r"(m));
             if (OP == 6) {
                 asm volatile("add.u32 %0, %0, %1;" : "+r"(x[i]) : "r"(m));
                 asm volatile("mad.lo.u32 %0, %0, %1, %2;" : "+r"(y[i]) : "r"(m), "r"(a0));
@@ -194,6 +201,9 @@ int main() {
     raw("prmt", 1, time_ms([&] { k_raw<4><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
     raw("add.cc + addc", 2, time_ms([&] { k_raw<5><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
     raw("add.u32 + mad.lo.u32", 2, time_ms([&] { k_raw<6><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("mad.wide.s32", 1, time_ms([&] { k_raw<7><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("mul.wide.s32 + add.s64", 1, time_ms([&] { k_raw<8><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
+    raw("mad.lo.s32", 1, time_ms([&] { k_raw<9><<<GRID, BLOCK>>>((uint32_t*)d, 12345, 77); }));
     auto fld = [&](const char* name, int per, float ms) {
         double ops = threads * (ITERS / 4) * per;
         printf("%-28s %8.3f ms %9.1f Gop/s\n", name, ms, ops / ms / 1e6);

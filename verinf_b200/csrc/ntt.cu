@@ -31,6 +31,16 @@
 #include "kquant.cuh"
 #include "ntt_lanes.cuh"
 
+// Lane-form variants of the tile passes (k_pass_q, k_encode_mid_q; arithmetic of gl_lanes.cuh) are
+// compiled in only with -DVI_LANES=1.  They are bit-identical and execute 16-17 % fewer
+// instructions, spread over both integer pipes, but hold 64 data registers per thread, run at 16
+// warps per SM and came out 11-18 % slower than the 64-bit kernels on B200 (pass 1 / middle / pass 3 of
+// a 4096 x 2^16 -> 2^18 encode: 2.31 / 12.1 / 6.68 ms against 2.04 / 10.25 / 5.99 ms), so the default
+// build leaves them out.
+#ifndef VI_LANES
+#define VI_LANES 0
+#endif
+
 namespace {
 
 using vgl::add;
@@ -344,6 +354,9 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
 #ifndef VI_PASSQ_MINB
 #define VI_PASSQ_MINB 2
 #endif
+#ifndef VI_MIDQ_MINB
+#define VI_MIDQ_MINB 2
+#endif
 
 // The tile pass of k_pass in lane form (gl_lanes.cuh), for the plain loaders (LD = 0): values are
 // converted from the canonical 64-bit form as they are loaded and back as they are stored; the
@@ -514,6 +527,9 @@ struct MidArgs {
     const uint64_t* cscale;  // K entries: K^-1 * 7^l
     const uint64_t* twRL;    // w_{rho*L}^e, e < rho*L (stage-0 twiddles of the coset transforms)
     const uint64_t* fsN;     // N entries: fsN[kk*n1 + l2] = w_N^(l2*kk), kk = rho*m1 + t
+    // lane-form kernel (k_encode_mid_q): the same tables as balanced 24-bit digits
+    const vln::W3 *twL3, *cscale3, *twRL3, *fsN3;
+    vln::W3 k_inv3;
 };
 
 // x * 2^E mod p for a compile-time E in [0, 192) (2^96 = -1)
@@ -648,6 +664,88 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     }
 }
 
+// v[j] = c[j] * w_{16*RHO}^(T*j) in lane form (lane rotations and at most one lane shift each)
+template <int RHO, int T, int J = 0>
+__device__ __forceinline__ void coset_shift_q(const uint64_t (&c)[16], vln::Q (&v)[16]) {
+    if constexpr (J < 16) {
+        constexpr int E = (vdft::root_exp(RHO == 4 ? 6 : RHO == 2 ? 5 : 4) * T * J) % 192;
+        v[J] = vln::mul_pow2<E>(vln::from_u64(c[J]));
+        coset_shift_q<RHO, T, J + 1>(c, v);
+    }
+}
+
+// The shift-twist middle pass (k_encode_mid<LOGL, RHO>, RHO = 2 or 4) in lane form, for tile lengths
+// from 128 points (every tile is full).  The scaled coefficients are kept between the cosets in
+// canonical 64-bit form (32 registers instead of 64) and unpacked per coset.
+template <int LOGL, int RHO>
+__global__ void __launch_bounds__(tile_max_threads(LOGL), LOGL <= 8 ? VI_MIDQ_MINB : 1) k_encode_mid_q(MidArgs a) {
+    using SI = Sched<LOGL, false>;   // inverse: small stage first, radix-16 last
+    using SF = Sched<LOGL, true>;    // forward: radix-16 first, small stage last
+    using vln::Q;
+    constexpr int L = 1 << LOGL, EPT = SI::EPT;
+    constexpr int LR = SI::logr(SI::NS - 1);   // last inverse radix == first forward radix
+    static_assert(LOGL >= 7 && (RHO == 2 || RHO == 4) && EPT == 16, "lane-form middle pass: full 16-column tiles");
+    extern __shared__ int4 smq[];
+    constexpr int logC = fixed_logC(LOGL), C = 1 << logC, CP = C + 1;
+    const int tid = threadIdx.x;
+    const int col = tid & (C - 1), w = tid >> logC;
+    const uint32_t tpi = (uint32_t)a.tiles_per_item;
+    const uint32_t item32 = blockIdx.x / tpi;
+    const int64_t item = item32;
+    const int64_t col0 = (int64_t)(blockIdx.x - item32 * tpi) * C;
+    const int64_t colg = col0 + col;
+    const uint32_t n1 = (uint32_t)a.n1;
+    {
+        const int nthr = blockDim.x;
+        const uint64_t* src = a.s1 + item * a.K + col0 * L;
+        if (logC == 4) {
+#pragma unroll
+            for (int cl = 0; cl < 16; ++cl) vlt::sts_q(smq, tid * 17 + cl, vln::from_u64(src[cl * L + tid]));
+        } else {
+            for (int e = tid; e < L * C; e += nthr) {
+                const int idx = e & (L - 1), cl = e >> LOGL;
+                vlt::sts_q(smq, idx * CP + cl, vln::from_u64(src[(uint32_t)(cl * L + idx)]));
+            }
+        }
+        __syncthreads();
+    }
+    Q v[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) v[j] = vlt::lds_q(smq, SI::first_pos(j, w) * CP + col);
+    vlt::run_stages_q<SI, LOGL, true, 0>(v, smq, CP, col, w, a.twL3);
+    if (a.polys) {
+        uint64_t* dst = a.polys + item * a.K + colg;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) dst[(uint32_t)SI::last_k(j, w) * n1] = vln::to_u64(vln::mul(v[j], a.k_inv3));
+    }
+    if (!a.s2) return;
+    uint64_t* dst2 = a.s2 + item * a.K * a.rho + colg;
+    // c2[j] = coefficient l1 = first_pos(j) (held in v[brev(j)]) times K^-1 7^l, l = l1*n1 + l2
+    uint64_t c2[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const uint32_t l1 = SF::first_pos(j, w);
+        c2[j] = vln::to_u64(vln::mul(v[brev(j, LR)], vlt::ldg_w3(a.cscale3 + colg + n1 * l1)));
+    }
+#pragma unroll 1
+    for (int t = 0; t < RHO; ++t) {
+        __syncthreads();   // previous coset (or the inverse transform) finished reading the tile
+        switch (t) {
+            case 0: coset_shift_q<RHO, 0>(c2, v); break;
+            case 1: coset_shift_q<RHO, 1>(c2, v); break;
+            case 2: coset_shift_q<RHO, 2 % RHO>(c2, v); break;
+            default: coset_shift_q<RHO, 3 % RHO>(c2, v); break;
+        }
+        vlt::run_stages_q<SF, LOGL, false, 0, RHO>(v, smq, CP, col, w, a.twL3, a.twRL3, t);
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const uint32_t m1 = SF::last_k(j, w);
+            const uint32_t kk = m1 * RHO + (uint32_t)t;
+            dst2[kk * n1] = vln::to_u64(vln::mul(v[j], vlt::ldg_w3(a.fsN3 + colg + kk * n1)));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Host side: twiddle cache, launch planning.
 // ---------------------------------------------------------------------------
@@ -718,10 +816,12 @@ int get_tw(int64_t n, const uint64_t** out) {
     int rc_up = upload_table(h, &d);
     if (rc_up) return rc_up;
     vln::W3* d3 = nullptr;
+#if VI_LANES
     rc_up = upload_w3(h, &d3);
     if (rc_up) { cudaFree(d); return rc_up; }
+#endif
     T.tw[n] = d;
-    T.w3[d] = d3;
+    if (d3) T.w3[d] = d3;
     *out = d;
     return VI_OK;
 }
@@ -750,10 +850,12 @@ int get_fs(int64_t n, int64_t ncols, bool inv, const uint64_t** out) {
     int rc_up = upload_table(h, &d);
     if (rc_up) return rc_up;
     vln::W3* d3 = nullptr;
+#if VI_LANES
     rc_up = upload_w3(h, &d3);
     if (rc_up) { cudaFree(d); return rc_up; }
+#endif
     T.fs[key] = d;
-    T.w3[d] = d3;
+    if (d3) T.w3[d] = d3;
     *out = d;
     return VI_OK;
 }
@@ -795,7 +897,13 @@ int get_cscale(int64_t K, const uint64_t** out) {
     uint64_t* d = nullptr;
     int rc_up = upload_table(h, &d);
     if (rc_up) return rc_up;
+    vln::W3* d3 = nullptr;
+#if VI_LANES
+    rc_up = upload_w3(h, &d3);
+    if (rc_up) { cudaFree(d); return rc_up; }
+#endif
     T.cscale[K] = d;
+    if (d3) T.w3[d] = d3;
     *out = d;
     return VI_OK;
 }
@@ -820,11 +928,6 @@ int tile_threads(int logL, int logC) {
 }
 size_t tile_smem(int logL, int logC) { return (size_t)(1 << logL) * ((1 << logC) + 1) * 8; }
 
-// Lane-form passes are used for the plain loaders of tile lengths 2^4 .. 2^10 (VI_LANES=0 builds the
-// library without them).
-#ifndef VI_LANES
-#define VI_LANES 1
-#endif
 template <int LOGL, bool INV, int MODE>
 int launch_pass_q(const PassArgs& a, int64_t items, cudaStream_t st, int tag) {
     size_t smem = 2 * tile_smem(LOGL, a.logC);
@@ -911,7 +1014,28 @@ int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
 bool mid_shift_form(int logL, int64_t rho) {
     return (rho == 2 || rho == 4) && logL >= 4 && logL <= 10;
 }
+template <int LOGL, int RHO>
+int launch_mid_q(const MidArgs& a, int64_t items, cudaStream_t st) {
+    size_t smem = 2 * tile_smem(LOGL, a.logC);
+    auto fn = k_encode_mid_q<LOGL, RHO>;
+    if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t grid = items * a.tiles_per_item;
+    if (grid <= 0) return VI_OK;
+    if (grid > 0x7FFFFFFFLL) return vi::fail(VI_ERR_LIMIT, "tile grid too large (%lld)", (long long)grid);
+    vi::ProfScope prof(vi::PROF_ENC_MID, st);
+    fn<<<(unsigned)grid, tile_threads(LOGL, a.logC), smem, st>>>(a);
+    return vi::check_launch("k_encode_mid_q");
+}
 int launch_mid(int logL, const MidArgs& a, int64_t items, cudaStream_t st) {
+#if VI_LANES
+    if (mid_shift_form(logL, a.rho) && logL >= 7 && a.twL3 && a.cscale3 && a.twRL3 && a.fsN3) {
+        switch (logL * 8 + a.rho) {
+#define VI_CASE(x) case x * 8 + 2: return launch_mid_q<x, 2>(a, items, st); case x * 8 + 4: return launch_mid_q<x, 4>(a, items, st);
+            VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10)
+#undef VI_CASE
+        }
+    }
+#endif
     if (mid_shift_form(logL, a.rho)) {
         switch (logL * 8 + a.rho) {
 #define VI_CASE(x) case x * 8 + 2: return launch_mid_t<x, 2>(a, items, st); case x * 8 + 4: return launch_mid_t<x, 4>(a, items, st);
@@ -1166,6 +1290,11 @@ static int encode_impl(const uint64_t* msg, const KqSrc* kq, int64_t m, int64_t 
         mid.cscale = cscale; mid.twRL = twRL; mid.fsN = fsN;
         rc = get_tw(n2, &mid.twL);
         if (rc) return rc;
+        mid.twL3 = w3_of(mid.twL);
+        mid.cscale3 = cscale ? w3_of(cscale) : nullptr;
+        mid.twRL3 = twRL ? w3_of(twRL) : nullptr;
+        mid.fsN3 = fsN ? w3_of(fsN) : nullptr;
+        mid.k_inv3 = vln::make_w3(mid.k_inv);
         rc = launch_mid(log2, mid, cnt, st);
         if (rc) return rc;
         if (!codes) continue;

@@ -38,9 +38,14 @@ __device__ __forceinline__ W3 tw3_at(const W3* __restrict__ tw, uint32_t e, uint
 
 // Stages S..NS-1 of the tile DFT on lane-form registers; v is preloaded for stage S and holds the
 // outputs of the last stage on return (Sched::last_k).  SC is the Sched<LOGL, SMALL_LAST> of ntt.cu.
-template <class SC, int LOGL, bool INV, int S>
+// RHO0 > 0 (forward only): the transform is coset t of a length RHO0*L transform whose input was
+// pre-multiplied by w_{RHO0*L}^(t*l) except for the factor common to a thread's first butterfly,
+// w_{RHO0*L}^(t*qp); that factor is folded into the stage-0 twiddle: w_L^(qp*c) * w_{RHO0*L}^(t*qp)
+// = tw0[qp*(RHO0*c + t)] with tw0 the table of w_{RHO0*L} (every output is multiplied, also c = 0).
+template <class SC, int LOGL, bool INV, int S, int RHO0 = 0>
 __device__ __forceinline__ void run_stages_q(Q (&v)[SC::EPT], int4* sm, int CP, int col, int w,
-                                             const W3* __restrict__ twL) {
+                                             const W3* __restrict__ twL, const W3* __restrict__ tw0 = nullptr,
+                                             int t = 0) {
     if constexpr (S < SC::NS) {
         constexpr int LOGR = SC::logr(S), R = 1 << LOGR, G = SC::EPT / R, LOGP = SC::logp(S);
         constexpr int L = 1 << LOGL, PP = 1 << LOGP;
@@ -58,11 +63,20 @@ __device__ __forceinline__ void run_stages_q(Q (&v)[SC::EPT], int4* sm, int CP, 
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 const uint32_t qp = (uint32_t)(w + g * SC::TPC) >> LOGP;
-                v[g * R] = vln::renorm(v[g * R]);         // output 0 has no twiddle: only bring its lanes back
+                if constexpr (S == 0 && RHO0 > 0) {
+                    static_assert(!INV && LOGP == 0, "coset twiddles: forward stage 0 only");
 #pragma unroll
-                for (int c = 1; c < R; ++c) {
-                    const uint32_t e = (qp * c) << LOGP;
-                    v[g * R + vdft::brev(c, LOGR)] = vln::mul(v[g * R + vdft::brev(c, LOGR)], tw3_at<INV>(twL, e, L - 1));
+                    for (int c = 0; c < R; ++c)
+                        v[g * R + vdft::brev(c, LOGR)] =
+                            vln::mul(v[g * R + vdft::brev(c, LOGR)], ldg_w3(tw0 + qp * (uint32_t)(RHO0 * c + t)));
+                } else {
+                    v[g * R] = vln::renorm(v[g * R]);     // output 0 has no twiddle: only bring its lanes back
+#pragma unroll
+                    for (int c = 1; c < R; ++c) {
+                        const uint32_t e = (qp * c) << LOGP;
+                        v[g * R + vdft::brev(c, LOGR)] =
+                            vln::mul(v[g * R + vdft::brev(c, LOGR)], tw3_at<INV>(twL, e, L - 1));
+                    }
                 }
             }
             __syncthreads();
@@ -75,7 +89,7 @@ __device__ __forceinline__ void run_stages_q(Q (&v)[SC::EPT], int4* sm, int CP, 
                     sts_q(sm, (qp * PP * R + kappa + PP * c) * CP + col, v[g * R + vdft::brev(c, LOGR)]);
             }
             __syncthreads();
-            run_stages_q<SC, LOGL, INV, S + 1>(v, sm, CP, col, w, twL);
+            run_stages_q<SC, LOGL, INV, S + 1, RHO0>(v, sm, CP, col, w, twL, tw0, t);
         }
     }
 }
