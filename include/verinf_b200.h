@@ -255,6 +255,16 @@ int vi_gl_matmul(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, i
 int64_t vi_gl_matmul_tc_scratch_bytes(int64_t m, int64_t k, int64_t n);
 int vi_gl_matmul_tc(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n,
                     void* scratch, int64_t scratch_bytes, void* stream);
+/* The same product on the 5th-generation tensor cores (tcgen05.mma kind::i8, M128 x N256 x K32) with
+ * the 15 plane-sum accumulators of a 128 x 32 output tile in tensor memory and the byte planes
+ * brought in by TMA (no counterpart in the reference; replaces prover/kernels/gl_matmul.cuh:28-59
+ * for large products).  scratch: vi_gl_matmul_umma_scratch_bytes(m, k, n) bytes, 256-byte aligned.
+ * status_dev: optional device int32, cleared on the stream before the launch; the kernel sets it
+ * non-zero if one of its bounded waits expired (it then frees its tensor memory and returns; C is
+ * incomplete).  Read it after synchronising the stream.  Bit-identical to vi_gl_matmul. */
+int64_t vi_gl_matmul_umma_scratch_bytes(int64_t m, int64_t k, int64_t n);
+int vi_gl_matmul_umma(const uint64_t* A, const uint64_t* B, uint64_t* C, int64_t m, int64_t k, int64_t n,
+                      void* scratch, int64_t scratch_bytes, int32_t* status_dev, void* stream);
 int vi_gl_matvec(const uint64_t* M, const uint64_t* v, uint64_t* w, int64_t m, int64_t n, void* stream);
 int vi_gl_spmv(const uint64_t* values, const uint64_t* col_idx, const uint64_t* row_ptr,
                const uint64_t* x, const uint8_t* seed_dev, const uint8_t* label_dev, int label_len,

@@ -675,6 +675,50 @@ def test_matmul_tensor_cores_vs_oracle(cp, m, k, n):
     assert np.array_equal(_matmul_tc(A, B), oracle.gl_matmul(A, B))
 
 
+def _matmul_umma(A, B):
+    """vi_gl_matmul_umma through the C ABI, with its device status word checked."""
+    from verinf_b200._lib import LIB, check, ptr, stream_ptr
+    m, k = A.shape
+    n = B.shape[1]
+    nb = LIB.vi_gl_matmul_umma_scratch_bytes(m, k, n)
+    sc = torch.empty(max(nb, 256), dtype=torch.uint8, device="cuda")
+    st = torch.full((1,), 77, dtype=torch.int32, device="cuda")
+    out = torch.empty((m, n), dtype=torch.uint64, device="cuda")
+    a_d, b_d = dev(A), dev(B)
+    check(LIB.vi_gl_matmul_umma(ptr(a_d), ptr(b_d), ptr(out), m, k, n, ptr(sc), nb, ptr(st), stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0, "a bounded wait of the tcgen05 kernel expired"
+    return host(out)
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 64, 32), (1, 1, 1), (3, 5, 2), (70, 2100, 45), (130, 4096, 64), (65, 4097, 33),
+                                   (16, 9000, 40), (200, 300, 500), (257, 8193, 31)])
+def test_matmul_tcgen05_vs_oracle(cp, m, k, n):
+    """byte-plane product with tensor-memory accumulators (tcgen05.mma kind::i8): ragged tiles, k not a
+    multiple of the 64-byte stage, several 4096-term chunks (accumulators restarted per chunk)"""
+    rng = np.random.default_rng(m * 11 + k + n)
+    A, B = rnd_field(rng, (m, k)), rnd_field(rng, (k, n))
+    assert np.array_equal(_matmul_umma(A, B), oracle.gl_matmul(A, B))
+
+
+def test_matmul_tcgen05_extreme_operands_and_dispatch(cp):
+    # every byte 0xff where the field allows it: all 15 plane sums reach their bound within a chunk
+    A = np.full((128, 8192), 0xFFFFFFFEFFFFFFFF, dtype=np.uint64)
+    B = np.full((8192, 32), 0xFFFFFFFEFFFFFFFF, dtype=np.uint64)
+    assert np.array_equal(_matmul_umma(A, B), oracle.gl_matmul(A, B))
+    A[:] = np.uint64(P - 1)
+    assert np.array_equal(_matmul_umma(A, B), oracle.gl_matmul(A, B))
+    # the Python entry point takes this path from 2^26 multiply-adds; all three kernels agree
+    rng = np.random.default_rng(2)
+    A, B = rnd_field(rng, (520, 1030)), rnd_field(rng, (1030, 260))
+    got = cp.gl_matmul(dev(A), dev(B))
+    assert torch.equal(got.view(torch.int64), cp.gl_matmul(dev(A), dev(B), path="umma").view(torch.int64))
+    assert torch.equal(got.view(torch.int64), cp.gl_matmul(dev(A), dev(B), path="mma").view(torch.int64))
+    assert torch.equal(got.view(torch.int64), cp.gl_matmul(dev(A), dev(B), path="simt").view(torch.int64))
+    cp.check_async_errors()
+    assert np.array_equal(host(got)[:7], oracle.gl_matmul(A[:7], B))
+
+
 def test_matmul_tensor_cores_extreme_operands(cp):
     # every byte 0xff where the field allows it: all 15 plane sums reach their bound within a chunk
     A = np.full((64, 8192), 0xFFFFFFFEFFFFFFFF, dtype=np.uint64)

@@ -58,6 +58,8 @@ SIGNATURES = {
     "vi_gl_matmul": (_int, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "vi_gl_matmul_tc_scratch_bytes": (_i64, [_i64, _i64, _i64]),
     "vi_gl_matmul_tc": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _i64, _p]),
+    "vi_gl_matmul_umma_scratch_bytes": (_i64, [_i64, _i64, _i64]),
+    "vi_gl_matmul_umma": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _i64, _p, _p]),
     "vi_gl_matvec": (_int, [_p, _p, _p, _i64, _i64, _p]),
     "vi_gl_spmv": (_int, [_p, _p, _p, _p, _p, _p, _int, _p, _i64, _p]),
     "vi_lookup_multiplicities": (_int, [_p, _i64, _p, _i64, _p, _p]),

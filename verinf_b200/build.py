@@ -7,7 +7,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 SO = HERE / "libverinf_b200.so"
-SOURCES = ["common.cu", "ntt.cu", "hash.cu", "field_ops.cu", "kquant.cu", "sumcheck.cu", "open.cu", "matmul_tc.cu"]
+SOURCES = ["common.cu", "ntt.cu", "hash.cu", "field_ops.cu", "kquant.cu", "sumcheck.cu", "open.cu", "matmul_tc.cu", "matmul_umma.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -269,7 +269,26 @@ def poly_mul_batched(A, B):
 _TC_MIN_MACS = 1 << 22      # below this the plane split costs more than it saves
 
 
-def gl_matmul(A, B, force_simt=False):
+_UMMA_MIN_MACS = 1 << 26    # from here the tcgen05 kernel (128 x 32 tiles, tensor-memory accumulators) wins
+_umma_status = {}           # device index -> int32 tensor the last tcgen05 launch reports into
+
+
+def check_async_errors():
+    """Raises if a tcgen05 matmul launched earlier gave up on one of its bounded waits (its output is
+    then incomplete).  Synchronises the devices it checks; gl_matmul itself checks the previous
+    launch's status lazily, before it starts the next one."""
+    for idx, st in list(_umma_status.items()):
+        code = int(st.item())
+        if code:
+            st.zero_()
+            raise RuntimeError(f"gl_matmul (tcgen05 path) on cuda:{idx}: a device-side wait expired (code {code}); "
+                               "the product written by that call is incomplete")
+
+
+def gl_matmul(A, B, force_simt=False, path=None):
+    """C = A.B mod p.  `path` forces a kernel ("simt", "mma", "umma"); by default products of at most
+    4 rows stream B once, small ones use the scalar-pipe kernel, larger ones the integer tensor
+    cores (mma.sync tiles, and from 2^26 multiply-adds the tcgen05 kernel)."""
     _chk_u64(A, "A"); _chk_u64(B, "B")
     if A.dim() != 2 or B.dim() != 2:
         raise RuntimeError("gl_matmul: 2-D inputs")
@@ -281,7 +300,21 @@ def gl_matmul(A, B, force_simt=False):
         # the tensor-core launch covers m < 65535 * 64 rows and k < 65535 * 32; beyond that (which the
         # reference's kernel accepts) the scalar-pipe kernel takes any m and k < 2^32
         tc_fits = (m + 63) // 64 <= 65535 and (k + 63) // 64 * 2 <= 65535
-        if m > 4 and n > 1 and m * k * n >= _TC_MIN_MACS and tc_fits and not force_simt:
+        if force_simt:
+            path = "simt"
+        if path is None:
+            big = m > 4 and n > 1 and tc_fits
+            path = "umma" if big and m * k * n >= _UMMA_MIN_MACS and 8 * max(m, n) < (1 << 30) else \
+                "mma" if big and m * k * n >= _TC_MIN_MACS else "simt"
+        if path == "umma":
+            idx = A.device.index if A.device.index is not None else torch.cuda.current_device()
+            st = _umma_status.get(idx)
+            if st is None:
+                st = _umma_status[idx] = torch.zeros(1, dtype=torch.int32, device=A.device)
+            nb = LIB.vi_gl_matmul_umma_scratch_bytes(m, k, n)
+            sc = scratch(nb, A.device, "matmul")
+            check(LIB.vi_gl_matmul_umma(ptr(A), ptr(B), ptr(Cm), m, k, n, ptr(sc), nb, ptr(st), stream_ptr()))
+        elif path == "mma":
             # large products: byte planes on the integer tensor cores (same result)
             nb = LIB.vi_gl_matmul_tc_scratch_bytes(m, k, n)
             sc = scratch(nb, A.device, "matmul")

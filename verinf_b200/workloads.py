@@ -120,7 +120,12 @@ def field_matmul(dev, m=1000, k=4096, n=11008, seed=5):
     X = _rand_int8_field((m, k), g, dev)
     W = _rand_int8_field((k, n), g, dev)
     ms = _event_ms(lambda: cp.gl_matmul(X, W))
-    return {"m": m, "k": k, "n": n, "ms": ms, "multiply_adds_per_s": m * k * n / ms * 1e3}
+    out = {"m": m, "k": k, "n": n, "ms": ms, "multiply_adds_per_s": m * k * n / ms * 1e3}
+    if m > 4 and n > 1:
+        out["mma_sync_ms"] = _event_ms(lambda: cp.gl_matmul(X, W, path="mma"))
+        out["tcgen05_ms"] = _event_ms(lambda: cp.gl_matmul(X, W, path="umma"))
+        cp.check_async_errors()
+    return out
 
 
 def fold_products(dev, rows=1024, k_deg=K_DEG, seed=9):
