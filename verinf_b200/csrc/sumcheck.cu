@@ -232,6 +232,85 @@ __global__ void __launch_bounds__(BLOCK) k_sumcheck_finish(const uint64_t* __res
     }
 }
 
+// All remaining rounds of a queued run in ONE launch of one CTA, once the tables are small: below a
+// few thousand entries a round is two launches of ~3.5 us of pure latency (the 2^24 instance spends
+// 13 of its 24 rounds there), while one CTA folds and evaluates such a table in well under that.
+// Rounds rnd0 .. n_rounds-1 are produced (round rnd0 without a fold when rnd0 == 0), then the last
+// fold; samples and the skipped g(1) follow the conventions of vi_sumcheck_run.
+constexpr int TAIL_BLOCK = 512;
+constexpr int64_t TAIL_SIZE = 1 << 13;      // table length (before the pending fold) from which the tail kernel takes over
+constexpr int TAIL_MAX_ROUNDS = 16;
+struct TailCoins { uint64_t c[TAIL_MAX_ROUNDS]; };
+
+template <int NT>
+__global__ void __launch_bounds__(TAIL_BLOCK) k_sumcheck_tail(Problem pb, int64_t size, int rnd0, int n_rounds,
+                                                              TailCoins coins, uint64_t* __restrict__ samples) {
+    constexpr int NS = NT + 1;
+    __shared__ uint64_t red[TAIL_BLOCK / 32][NS];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    for (int rnd = rnd0; rnd < n_rounds; ++rnd) {
+        const bool fold = rnd > 0;
+        const uint64_t r = fold ? coins.c[rnd - rnd0] : 0;          // coins.c[j] = challenge of round rnd0 + j - 1
+        const int64_t items = fold ? size / 4 : size / 2, q = items;
+        uint64_t acc[NS];
+#pragma unroll
+        for (int x = 0; x < NS; ++x) acc[x] = 0;
+        for (int64_t i = tid; i < items; i += TAIL_BLOCK) {
+            uint64_t cur[NT], d[NT];
+#pragma unroll
+            for (int k = 0; k < NT; ++k) {
+                uint64_t* f = pb.tab[k];
+                uint64_t lo, hi;
+                if (!fold) { lo = f[i]; hi = f[i + q]; }
+                else {
+                    const uint64_t a0 = f[i], b0 = f[i + q], a1 = f[i + 2 * q], b1 = f[i + 3 * q];
+                    lo = add(a0, mul(r, sub(a1, a0)));
+                    hi = add(b0, mul(r, sub(b1, b0)));
+                    f[i] = lo;
+                    f[i + q] = hi;
+                }
+                cur[k] = lo;
+                d[k] = sub(hi, lo);
+            }
+#pragma unroll
+            for (int x = 0; x < NS; ++x) {
+                if (!(fold && x == 1)) {                 // g(1) of a folded round follows from g(0) + g(1) = g_prev(r)
+                    uint64_t prod = cur[0];
+#pragma unroll
+                    for (int k = 1; k < NT; ++k) prod = mul(prod, cur[k]);
+                    acc[x] = add(acc[x], prod);
+                }
+                if (x + 1 < NS) {
+#pragma unroll
+                    for (int k = 0; k < NT; ++k) cur[k] = add(cur[k], d[k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < NS; ++x) {
+            uint64_t v = acc[x];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v = add(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (lane == 0) red[wid][x] = v;
+        }
+        __syncthreads();
+        if (tid < NS) {
+            uint64_t v = 0;
+#pragma unroll
+            for (int w = 0; w < TAIL_BLOCK / 32; ++w) v = add(v, red[w][tid]);
+            samples[(int64_t)rnd * 8 + tid] = v;
+        }
+        if (fold) size /= 2;
+        __syncthreads();          // folded entries (global memory) and `red` are reused by the next round
+    }
+    // last fold: size 2 -> 1
+    if (tid < NT) {
+        uint64_t* f = pb.tab[tid];
+        const uint64_t r = coins.c[n_rounds - rnd0];
+        f[0] = add(f[0], mul(r, sub(f[1], f[0])));
+    }
+}
+
 // last fold: size 2 -> 1, no samples
 __global__ void k_final_fold(Problem pb, uint64_t r) {
     int k = threadIdx.x;
@@ -338,6 +417,30 @@ extern "C" int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, i
     VI_REQUIRE(n_rounds == 0 || (coins && samples), "sumcheck_run: null pointer");
     int64_t cur = size;
     for (int rnd = 0; rnd < n_rounds; ++rnd) {
+        if (cur <= TAIL_SIZE && n_rounds - rnd + 1 <= TAIL_MAX_ROUNDS) {
+            // small tables: one single-CTA launch does rounds rnd .. n_rounds-1 and the last fold
+            Problem pb;
+            int rc = make_problem(pb, tables, stride, n_tables, n_terms, coefs, nfac, fac);
+            if (rc) return rc;
+            if (pb.simple) {
+                VI_REQUIRE(samples && partials, "sumcheck: null output/scratch");
+                TailCoins tc{};
+                for (int j = 0; j <= n_rounds - rnd; ++j) {           // c[j] = challenge of round rnd + j - 1
+                    const int idx = rnd + j - 1;
+                    tc.c[j] = idx >= 0 ? coins[idx] : 0;
+                    VI_REQUIRE(tc.c[j] < vgl::P, "sumcheck: challenge not canonical");
+                }
+                cudaStream_t st = (cudaStream_t)stream;
+                vi::ProfScope prof(vi::PROF_SUMCHECK, st);
+                switch (pb.n_tables) {
+                    case 1: k_sumcheck_tail<1><<<1, TAIL_BLOCK, 0, st>>>(pb, cur, rnd, n_rounds, tc, samples); break;
+                    case 2: k_sumcheck_tail<2><<<1, TAIL_BLOCK, 0, st>>>(pb, cur, rnd, n_rounds, tc, samples); break;
+                    case 3: k_sumcheck_tail<3><<<1, TAIL_BLOCK, 0, st>>>(pb, cur, rnd, n_rounds, tc, samples); break;
+                    default: k_sumcheck_tail<4><<<1, TAIL_BLOCK, 0, st>>>(pb, cur, rnd, n_rounds, tc, samples); break;
+                }
+                return vi::check_launch("k_sumcheck_tail");
+            }
+        }
         // rounds after the first skip the sample at x = 1 (flag 2): see the header
         int rc = vi_sumcheck_round(tables, stride, n_tables, cur, n_terms, coefs, nfac, fac, rnd > 0 ? 3 : 0,
                                    rnd > 0 ? coins[rnd - 1] : 0, samples + (int64_t)rnd * 8, partials, stream);
