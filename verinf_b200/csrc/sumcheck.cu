@@ -57,6 +57,46 @@ __device__ __forceinline__ void block_reduce(uint64_t (&acc)[MAX_SAMPLES], int n
     }
 }
 
+// block_reduce followed by the cross-CTA sum in the same launch: the CTA that draws the last ticket of
+// a wrapping counter (left at zero again for the next launch) adds all partial sums and writes
+// out[0..ns).  Used by the queued run, which clears the counter once per run; saves one launch per round.
+__device__ __forceinline__ void block_reduce_finish(uint64_t (&acc)[MAX_SAMPLES], int ns, uint64_t* partials,
+                                                    unsigned* counter, uint64_t* out) {
+    __shared__ uint64_t red2[BLOCK / 32][MAX_SAMPLES];
+    __shared__ int is_last;
+    block_reduce(acc, ns, partials);
+    __threadfence();                       // this CTA's partial sums are visible before its ticket is drawn
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicInc(counter, gridDim.x - 1) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    uint64_t tot[MAX_SAMPLES];
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) tot[x] = 0;
+    for (int b = threadIdx.x; b < (int)gridDim.x; b += BLOCK)
+#pragma unroll
+        for (int x = 0; x < MAX_SAMPLES; ++x)
+            if (x < ns) tot[x] = add(tot[x], __ldcg(partials + (int64_t)b * MAX_SAMPLES + x));
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int x = 0; x < MAX_SAMPLES; ++x) {
+        if (x < ns) {
+            uint64_t v = tot[x];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v = add(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (lane == 0) red2[wid][x] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < ns) {
+        uint64_t v = 0;
+#pragma unroll
+        for (int w = 0; w < BLOCK / 32; ++w) v = add(v, red2[w][threadIdx.x]);
+        out[threadIdx.x] = v;
+    }
+}
+
 // MODE 0: claim (sum of products at every index, one "sample")
 // MODE 1: round samples on the tables as they are (pairs i, i+half)
 // MODE 2: fold with r (size -> size/2, in place), then round samples of the folded tables
@@ -150,7 +190,8 @@ __global__ void __launch_bounds__(BLOCK) k_sumcheck(Problem pb, int64_t size, ui
 // no per-table runtime predicates), which lifts the occupancy limit of the general kernel.
 template <int MODE, int NT>
 __global__ void __launch_bounds__(BLOCK) k_sumcheck_simple(Problem pb, int64_t size, uint64_t r, int skip1,
-                                                           uint64_t* partials) {
+                                                           uint64_t* partials, unsigned* counter = nullptr,
+                                                           uint64_t* out = nullptr) {
     constexpr int NS = MODE == 0 ? 1 : NT + 1;
     const int64_t items = MODE == 0 ? size : MODE == 1 ? size / 2 : size / 4;
     const int64_t q = items;
@@ -190,16 +231,18 @@ __global__ void __launch_bounds__(BLOCK) k_sumcheck_simple(Problem pb, int64_t s
             }
         }
     }
-    block_reduce(acc, NS, partials);
+    if (counter) block_reduce_finish(acc, NS, partials, counter, out);
+    else block_reduce(acc, NS, partials);
 }
 
 template <int MODE>
-void launch_simple(const Problem& pb, int g, cudaStream_t st, int64_t size, uint64_t r, int skip1, uint64_t* partials) {
+void launch_simple(const Problem& pb, int g, cudaStream_t st, int64_t size, uint64_t r, int skip1, uint64_t* partials,
+                   unsigned* counter = nullptr, uint64_t* out = nullptr) {
     switch (pb.n_tables) {
-        case 1: k_sumcheck_simple<MODE, 1><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
-        case 2: k_sumcheck_simple<MODE, 2><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
-        case 3: k_sumcheck_simple<MODE, 3><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
-        default: k_sumcheck_simple<MODE, 4><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials); break;
+        case 1: k_sumcheck_simple<MODE, 1><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials, counter, out); break;
+        case 2: k_sumcheck_simple<MODE, 2><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials, counter, out); break;
+        case 3: k_sumcheck_simple<MODE, 3><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials, counter, out); break;
+        default: k_sumcheck_simple<MODE, 4><<<g, BLOCK, 0, st>>>(pb, size, r, skip1, partials, counter, out); break;
     }
 }
 
@@ -359,7 +402,8 @@ int grid_for(int64_t items) {
 
 }  // namespace
 
-extern "C" int64_t vi_sumcheck_scratch_bytes(void) { return (int64_t)MAX_GRID * MAX_SAMPLES * 8; }
+// per-CTA partial sums, then the ticket counter of the fused cross-CTA sum
+extern "C" int64_t vi_sumcheck_scratch_bytes(void) { return (int64_t)MAX_GRID * MAX_SAMPLES * 8 + 64; }
 
 extern "C" int vi_sumcheck_claim(const uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                                  int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
@@ -416,7 +460,31 @@ extern "C" int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, i
     VI_REQUIRE(vi::is_pow2(size) && (int64_t(1) << n_rounds) == size, "sumcheck_run: size must be 2^n_rounds");
     VI_REQUIRE(n_rounds == 0 || (coins && samples), "sumcheck_run: null pointer");
     int64_t cur = size;
+    unsigned* counter = partials ? (unsigned*)((char*)partials + (int64_t)MAX_GRID * MAX_SAMPLES * 8) : nullptr;
+    bool counter_clear = false;
     for (int rnd = 0; rnd < n_rounds; ++rnd) {
+        if (cur > TAIL_SIZE) {
+            // large rounds of the common case: the cross-CTA sum is fused into the round kernel
+            Problem pb;
+            int rc = make_problem(pb, tables, stride, n_tables, n_terms, coefs, nfac, fac);
+            if (rc) return rc;
+            if (pb.simple) {
+                VI_REQUIRE(samples && partials, "sumcheck: null output/scratch");
+                cudaStream_t st = (cudaStream_t)stream;
+                if (!counter_clear) { VI_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), st)); counter_clear = true; }
+                vi::ProfScope prof(vi::PROF_SUMCHECK, st);
+                uint64_t* out = samples + (int64_t)rnd * 8;
+                if (rnd == 0) launch_simple<1>(pb, grid_for(cur / 2), st, cur, 0, 0, (uint64_t*)partials, counter, out);
+                else {
+                    VI_REQUIRE(coins[rnd - 1] < vgl::P, "sumcheck: challenge not canonical");
+                    launch_simple<2>(pb, grid_for(cur / 4), st, cur, coins[rnd - 1], 1, (uint64_t*)partials, counter, out);
+                    cur /= 2;
+                }
+                rc = vi::check_launch("k_sumcheck<fused>");
+                if (rc) return rc;
+                continue;
+            }
+        }
         if (cur <= TAIL_SIZE && n_rounds - rnd + 1 <= TAIL_MAX_ROUNDS) {
             // small tables: one single-CTA launch does rounds rnd .. n_rounds-1 and the last fold
             Problem pb;
