@@ -489,7 +489,8 @@ def run_native(a):
         from verinf_b200 import workloads
         extra["field_matmul"] = workloads.field_matmul(dev)
         extra["fold_products"] = workloads.fold_products(dev)
-        extra["reference_cuda"] = reference_cuda_leg()
+        if world == 1:          # one GPU only: the reference's extension takes a minute or two to JIT-build
+            extra["reference_cuda"] = reference_cuda_leg()
     if a.extra:
         # MoE variant: 128 experts x (5120 x 8192) int8, 16 per GPU at 8 GPUs, one commitment per expert,
         # roots gathered; with fewer ranks every rank still commits 16 experts (rank r: 16r .. 16r+15)
