@@ -45,9 +45,11 @@ int vi_gl_axpy(uint64_t* y, uint64_t alpha, const uint64_t* x, int64_t n, void* 
 /* ---- NTT --------------------------------------------------------------------
  * replaces ntt_forward/ntt_inverse(_batched) (prover/cuda_primitives.py:347-409,
  * prover/kernels/ntt.cuh:310-770).  In place over m contiguous rows of length n
- * (power of two, 2 <= n <= 2^24), natural order in and out; the inverse scales by
+ * (power of two, 2 <= n <= 2^30), natural order in and out; the inverse scales by
  * n^-1.  Transforms longer than 1024 need scratch (any size >= n*8 bytes works;
- * vi_ntt_scratch_bytes gives the recommended size: the rows of a 1 GiB chunk). */
+ * vi_ntt_scratch_bytes gives the recommended size: the rows of a 1 GiB chunk).  Above
+ * 2^24 the transform runs as three tile passes, one row at a time, and needs 2*n*8 bytes
+ * (the reference's dispatch takes any power of two, prover/kernels/ntt.cuh:746-770). */
 int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n);
 int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
                    void* scratch, int64_t scratch_bytes, void* stream);

@@ -60,7 +60,8 @@ def test_argument_validation_without_gpu(lib):
     assert L.vi_ntt_batched(p, 1, 12, 0, None, 0, None) != 0 and "power of 2" in _err(lib)
     assert L.vi_ntt_batched(p, 1, 1, 0, None, 0, None) != 0
     assert L.vi_ntt_batched(p, -1, 16, 0, None, 0, None) != 0
-    assert L.vi_ntt_batched(p, 1, 1 << 25, 0, None, 0, None) != 0 and "exceeds" in _err(lib)
+    assert L.vi_ntt_batched(p, 1, 1 << 31, 0, None, 0, None) != 0 and "exceeds" in _err(lib)
+    assert L.vi_ntt_batched(p, 1, 1 << 25, 0, None, 0, None) != 0 and "scratch" in _err(lib)   # three passes: 2*n*8 bytes
     assert L.vi_ntt_batched(p, 0, 16, 0, None, 0, None) == 0                  # empty batch is fine
     assert L.vi_encode_rows(p, 1, 9, 8, 32, 0, None, 0, p, p, p, 1 << 20, None) != 0 and "ELL" in _err(lib)
     assert L.vi_encode_rows(p, 1, 8, 12, 48, 0, None, 0, p, p, p, 1 << 20, None) != 0

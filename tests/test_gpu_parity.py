@@ -106,6 +106,33 @@ def test_ntt_batched_vs_oracle(cp, logn, m):
     assert np.array_equal(host(y), oracle.ntt_batched(a, invert=True))
 
 
+@pytest.mark.parametrize("logn,m", [(25, 2), (26, 1)])
+def test_ntt_three_pass(cp, logn, m):
+    """Lengths above 2^24 (three tile passes, split four-step factor tables; the reference's dispatch
+    takes any power of two, prover/kernels/ntt.cuh:746-770): the whole transform of the last row against
+    the oracle, a sparse input against the closed form X[k] = sum_i v_i w_n^(j_i k) at sampled k (first
+    row), and the inverse round trip."""
+    n = 1 << logn
+    rng = np.random.default_rng(logn)
+    a = rnd_field(rng, (m, n))
+    x = dev(a)
+    cp.ntt_forward_batched(x)
+    assert np.array_equal(host(x)[m - 1], oracle.ntt(a[m - 1]))
+    cp.ntt_inverse_batched(x)
+    assert np.array_equal(host(x), a)
+    w = pow(7, (P - 1) // n, P)
+    pos = [0, 1, n // 3, n - 1, (5 << (logn - 3)) + 77]
+    vals = [int(v) for v in rnd_field(rng, len(pos))]
+    sp = np.zeros((1, n), dtype=np.uint64)
+    for j, v in zip(pos, vals):
+        sp[0, j] = v
+    y = dev(sp)
+    cp.ntt_forward_batched(y)
+    got = host(y)[0]
+    for k in [0, 1, 2, n // 2, n - 1] + [int(t) for t in rng.integers(0, n, size=200)]:
+        assert int(got[k]) == sum(v * pow(w, (j * k) % n, P) for j, v in zip(pos, vals)) % P, k
+
+
 def test_ntt_large_roundtrip_and_errors(cp):
     rng = np.random.default_rng(7)
     for logn, m in ((20, 2), (21, 1), (22, 2), (24, 1)):

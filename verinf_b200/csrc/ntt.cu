@@ -159,6 +159,7 @@ struct PassArgs {
     uint32_t out_k, out_col;
     const uint64_t* twL;     // w_L^e, e < L
     const uint64_t* fs;      // four-step factors, fs[k*ncols + col] = w_n^(+-col*k), or null
+    const uint64_t* fs_hi;   // split factor form (LD = 3, transforms above 2^24): w_n^(+-e) = fs[e & 8191] * fs_hi[e >> 13]
     uint64_t scale;          // multiply outputs by this unless 1
     int out_via_smem;        // outputs are contiguous along k: transpose through smem
     // SRC_MSG loader: input element (item=row, pos, col) is slot j = pos*in_idx + col of the
@@ -210,7 +211,9 @@ __host__ __device__ constexpr int tile_max_threads(int logl) { return (logl >= 4
 
 // LD selects the loader of a MODE 0 pass at compile time, so that the plain loaders do not carry the
 // registers, code and barrier of the others: 0 = plain rows or message rows without pad, 1 = message
-// rows with the PRG pad, 2 = K-quant lift (pad decided at run time)
+// rows with the PRG pad, 2 = K-quant lift (pad decided at run time), 3 = plain rows with the four-step
+// factor taken from two small tables (the first pass of a three-pass transform, whose full factor table
+// would have n entries)
 template <int LOGL, bool INV, int MODE, int LD = 0>
 __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 8) ? (MODE == 0 ? VI_PASS0_MINB : (LOGL == 8 ? VI_PASS_MINB_L8 : VI_PASS_MINB)) : 1) k_pass(PassArgs a) {
     using SC = Sched<LOGL, false>;
@@ -229,7 +232,7 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     const uint32_t ncols32 = (uint32_t)a.ncols;
     uint64_t v[EPT];
     if constexpr (MODE == 0) {
-        if (LD == 0 && a.src_kind == SRC_PLAIN) {
+        if ((LD == 0 || LD == 3) && a.src_kind == SRC_PLAIN) {
             const uint64_t* src = a.in + item * a.in_item + colg * (int64_t)a.in_col;
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
@@ -323,7 +326,12 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
     // shared memory only for the single-pass transform (rows contiguous along the output index).
     for (int j = 0; j < EPT; ++j) {
         uint32_t k = SC::last_k(j, w);
-        if constexpr (MODE == 0) {
+        if constexpr (MODE == 0 && LD == 3) {
+            if (valid) {
+                const uint64_t e = (uint64_t)k * (uint64_t)colg;       // < n
+                v[j] = mul(mul(v[j], __ldg(a.fs + (e & 8191))), __ldg(a.fs_hi + (e >> 13)));
+            }
+        } else if constexpr (MODE == 0) {
             if (valid) v[j] = mul(v[j], __ldg(a.fs + col0 + (k * ncols32 + (uint32_t)col)));
         } else if constexpr (INV) {
             if (a.scale != 1) v[j] = mul(v[j], a.scale);
@@ -755,6 +763,7 @@ struct DevTables {
     std::map<int64_t, uint64_t*> cscale;                      // K -> K^-1 * 7^l
     std::map<std::tuple<int64_t, int64_t, bool>, uint64_t*> fs;   // (n, ncols, inverse) -> four-step factors
     std::map<const uint64_t*, vln::W3*> w3;                   // table -> the same constants as balanced 24-bit digits
+    std::map<std::pair<int64_t, bool>, std::pair<uint64_t*, uint64_t*>> split;   // (n, inverse) -> (w^e, e < 8192; w^(8192 e))
 };
 std::mutex g_mu;
 std::map<int, DevTables> g_tables;
@@ -857,6 +866,33 @@ int get_fs(int64_t n, int64_t ncols, bool inv, const uint64_t** out) {
     T.fs[key] = d;
     if (d3) T.w3[d] = d3;
     *out = d;
+    return VI_OK;
+}
+
+// w_n^(+-e) as a product of two table entries: lo[e & 8191] * hi[e >> 13] (n > 8192)
+int get_split(int64_t n, bool inv, const uint64_t** lo, const uint64_t** hi) {
+    int dev;
+    VI_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto& T = g_tables[dev];
+    auto key = std::make_pair(n, inv);
+    auto it = T.split.find(key);
+    if (it != T.split.end()) { *lo = it->second.first; *hi = it->second.second; return VI_OK; }
+    uint64_t wn = vgl::hpow(7, (vgl::P - 1) / (uint64_t)n);
+    if (inv) wn = vgl::hpow(wn, vgl::P - 2);
+    std::vector<uint64_t> hl(8192), hh((size_t)(n >> 13));
+    uint64_t cur = 1;
+    for (size_t e = 0; e < hl.size(); ++e) { hl[e] = cur; cur = vgl::hmul(cur, wn); }
+    const uint64_t step = cur;       // w^8192
+    cur = 1;
+    for (size_t e = 0; e < hh.size(); ++e) { hh[e] = cur; cur = vgl::hmul(cur, step); }
+    uint64_t *dl = nullptr, *dh = nullptr;
+    int rc_up = upload_table(hl, &dl);
+    if (rc_up) return rc_up;
+    rc_up = upload_table(hh, &dh);
+    if (rc_up) { cudaFree(dl); return rc_up; }
+    T.split[key] = std::make_pair(dl, dh);
+    *lo = dl; *hi = dh;
     return VI_OK;
 }
 
@@ -978,6 +1014,16 @@ int launch_pass_l(int logL, const PassArgs& a, int64_t items, cudaStream_t st, i
             }
         }
     }
+    if constexpr (MODE == 0) {
+        if (a.fs_hi != nullptr) {       // first pass of a three-pass transform: split factor tables
+            switch (logL) {
+#define VI_CASE(x) case x: return launch_pass_t<x, INV, 0, 3>(a, items, st, tag);
+                VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5) VI_CASE(6)
+                VI_CASE(7) VI_CASE(8) VI_CASE(9) VI_CASE(10) VI_CASE(11) VI_CASE(12)
+#undef VI_CASE
+            }
+        }
+    }
     switch (logL) {
 #define VI_CASE(x) case x: return launch_pass_t<x, INV, MODE>(a, items, st, tag);
         VI_CASE(0) VI_CASE(1) VI_CASE(2) VI_CASE(3) VI_CASE(4) VI_CASE(5)
@@ -992,7 +1038,7 @@ int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaSt
     int rc = get_tw(int64_t(1) << logL, &a.twL);
     if (rc) return rc;
     a.twL3 = w3_of(a.twL);
-    a.fs3 = a.fs ? w3_of(a.fs) : nullptr;
+    a.fs3 = (a.fs && !a.fs_hi) ? w3_of(a.fs) : nullptr;
     a.scale3 = vln::make_w3(a.scale);
     if (inv) return mode ? launch_pass_l<true, 1>(logL, a, items, st, tag) : launch_pass_l<true, 0>(logL, a, items, st, tag);
     return mode ? launch_pass_l<false, 1>(logL, a, items, st, tag) : launch_pass_l<false, 0>(logL, a, items, st, tag);
@@ -1080,14 +1126,18 @@ extern "C" int vi_release_tables(void) {
         for (auto& t : kv.second.fs) cudaFree(t.second);
         for (auto& t : kv.second.cscale) cudaFree(t.second);
         for (auto& t : kv.second.w3) cudaFree(t.second);
+        for (auto& t : kv.second.split) { cudaFree(t.second.first); cudaFree(t.second.second); }
     }
     g_tables.clear();
     VI_CUDA(cudaSetDevice(cur));
     return VI_OK;
 }
 
+constexpr int THREE_PASS_MAX_LOG = 30;   // tile-relative offsets are 32-bit: n * 8 bytes per row up to 8 GiB
+
 extern "C" int64_t vi_ntt_scratch_bytes(int64_t m, int64_t n) {
     if (n <= (int64_t(1) << SINGLE_LOGL) || m <= 0) return 0;
+    if (n > (int64_t(1) << (2 * MAX_LOGL))) return 2 * n * 8;      // three passes, one row at a time, two buffers
     int64_t row = n * 8;
     int64_t rows = chunk_bytes() / row;
     if (rows < 1) rows = 1;
@@ -1101,11 +1151,58 @@ extern "C" int vi_ntt_batched(uint64_t* rows, int64_t m, int64_t n, int inverse,
     VI_REQUIRE(m >= 0, "ntt: negative row count");
     VI_REQUIRE(vi::is_pow2(n) && n >= 2, "NTT length must be a power of 2 >= 2 (got %lld)", (long long)n);
     int logn = vi::ilog2(n);
-    if (logn > 2 * MAX_LOGL) return vi::fail(VI_ERR_LIMIT, "NTT length 2^%d exceeds the supported 2^%d", logn, 2 * MAX_LOGL);
+    if (logn > THREE_PASS_MAX_LOG) return vi::fail(VI_ERR_LIMIT, "NTT length 2^%d exceeds the supported 2^%d", logn, THREE_PASS_MAX_LOG);
     if (m == 0) return VI_OK;
     VI_REQUIRE(rows != nullptr, "ntt: null data pointer");
     const bool inv = inverse != 0;
     const uint64_t scale = inv ? inv_pow2(logn) : 1;
+    if (logn > 2 * MAX_LOGL) {
+        // Three passes, row by row: n = n1 * na * nb.  Pass A: length-n1 transforms over the n2 = na*nb columns
+        // (stride n2), four-step factor w_n^(j2*k1) from the split tables, into s1[k1][j2].  Then the length-n2
+        // transform of every row k1 of s1 as the usual two passes (through s2), the last one writing
+        // X[k1 + n1*(k2a + na*k2b)] and applying n^-1 on the inverse.
+        const int log1 = (logn + 2) / 3, logm = logn - log1, loga = (logm + 1) / 2, logb = logm - loga;
+        const int64_t n1 = int64_t(1) << log1, n2 = int64_t(1) << logm, na = int64_t(1) << loga, nb = int64_t(1) << logb;
+        VI_REQUIRE(scratch != nullptr && scratch_bytes >= 2 * n * 8,
+                   "ntt: scratch of at least %lld bytes required (see vi_ntt_scratch_bytes)", (long long)(2 * n * 8));
+        uint64_t* s1 = (uint64_t*)scratch;
+        uint64_t* s2 = s1 + n;
+        const uint64_t *flo, *fhi, *fs2;
+        int rc = get_split(n, inv, &flo, &fhi);
+        if (rc) return rc;
+        rc = get_fs(n2, nb, inv, &fs2);
+        if (rc) return rc;
+        for (int64_t r = 0; r < m; ++r) {
+            PassArgs a{};
+            a.in = rows + r * n; a.out = s1;
+            a.logC = pick_logC(log1, n2);
+            a.ncols = n2;
+            a.in_item = 0; a.in_idx = (uint32_t)n2; a.in_col = 1;
+            a.out_item = 0; a.out_k = (uint32_t)n2; a.out_col = 1;
+            a.fs = flo; a.fs_hi = fhi; a.scale = 1; a.out_via_smem = 0; a.src_kind = SRC_PLAIN;
+            rc = launch_pass(log1, inv, 0, a, 1, st, vi::PROF_NTT_PASS);
+            if (rc) return rc;
+            PassArgs b{};
+            b.in = s1; b.out = s2;
+            b.logC = pick_logC(loga, nb);
+            b.ncols = nb;
+            b.in_item = n2; b.in_idx = (uint32_t)nb; b.in_col = 1;
+            b.out_item = n2; b.out_k = (uint32_t)nb; b.out_col = 1;
+            b.fs = fs2; b.scale = 1; b.out_via_smem = 0; b.src_kind = SRC_PLAIN;
+            rc = launch_pass(loga, inv, 0, b, n1, st, vi::PROF_NTT_PASS);
+            if (rc) return rc;
+            PassArgs c{};
+            c.in = s2; c.out = rows + r * n;
+            c.logC = pick_logC(logb, na);
+            c.ncols = na;
+            c.in_item = n2; c.in_idx = 1; c.in_col = (uint32_t)nb;
+            c.out_item = 1; c.out_k = (uint32_t)(n1 * na); c.out_col = (uint32_t)n1;
+            c.fs = nullptr; c.scale = scale; c.out_via_smem = 0; c.src_kind = SRC_PLAIN;
+            rc = launch_pass(logb, inv, 1, c, n1, st, vi::PROF_NTT_PASS);
+            if (rc) return rc;
+        }
+        return VI_OK;
+    }
     if (logn <= SINGLE_LOGL) {
         PassArgs a{};
         a.in = rows; a.out = rows;
