@@ -19,6 +19,7 @@
 #include "../../include/verinf_b200.h"
 #include "common.cuh"
 #include "gl.cuh"
+#include "plane_fold.cuh"
 
 namespace {
 
@@ -88,19 +89,6 @@ __device__ __forceinline__ void mma_u8(int32_t (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// x * 2^E mod p for a compile-time E in [0, 192) (2^96 = -1)
-template <int E>
-__device__ __forceinline__ uint64_t shl_mod(uint64_t x) {
-    if constexpr (E == 0) return x;
-    else if constexpr (E < 96) return vgl::mul_pow2<E>(x);
-    else return vgl::sub(0, vgl::mul_pow2<E - 96>(x));
-}
-// sum_s t[s] 2^(8s) mod p for 15 non-negative 32-bit sums
-template <int S = 0>
-__device__ __forceinline__ uint64_t combine15(const int32_t (&t)[15]) {
-    if constexpr (S == 15) return 0;
-    else return vgl::add(shl_mod<8 * S>((uint64_t)(uint32_t)t[S]), combine15<S + 1>(t));
-}
 
 template <int I, int J>
 __device__ __forceinline__ void mma_pairs(int32_t (&acc)[15][2][4], const uint32_t (&a)[4], const uint32_t (&b)[8][4]) {
@@ -191,10 +179,10 @@ __global__ void __launch_bounds__(256, 1) k_matmul_planes(const uint8_t* __restr
         for (int t = 0; t < 2; ++t)
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                int32_t ts[15];
+                uint32_t ts[15];
 #pragma unroll
-                for (int s = 0; s < 15; ++s) ts[s] = acc[s][t][q];
-                const uint64_t v = combine15(ts);
+                for (int s = 0; s < 15; ++s) ts[s] = (uint32_t)acc[s][t][q];
+                const uint64_t v = vpf::combine15(ts);
                 const int64_t r = row0 + wm * 16 + g + (q >> 1) * 8;
                 const int64_t c = col0 + wn * 16 + t * 8 + tig * 2 + (q & 1);
                 if (r < m && c < n) C[r * n + c] = c0k == 0 ? v : vgl::add(C[r * n + c], v);

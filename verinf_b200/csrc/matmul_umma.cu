@@ -25,6 +25,7 @@
 #include "../../include/verinf_b200.h"
 #include "common.cuh"
 #include "gl.cuh"
+#include "plane_fold.cuh"
 
 namespace {
 
@@ -136,18 +137,6 @@ __host__ __device__ constexpr uint32_t idesc_u8(int n) {
     return (2u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UM_TM >> 4) << 24);
 }
 
-// x * 2^E mod p for a compile-time E in [0, 192) (2^96 = -1)
-template <int E>
-__device__ __forceinline__ uint64_t shl_mod(uint64_t x) {
-    if constexpr (E == 0) return x;
-    else if constexpr (E < 96) return vgl::mul_pow2<E>(x);
-    else return vgl::sub(0, vgl::mul_pow2<E - 96>(x));
-}
-template <int S = 0>
-__device__ __forceinline__ uint64_t combine15(const uint32_t (&t)[15]) {
-    if constexpr (S == 15) return 0;
-    else return vgl::add(shl_mod<8 * S>((uint64_t)t[S]), combine15<S + 1>(t));
-}
 
 enum { UM_ERR_FULL = 1, UM_ERR_EMPTY = 2, UM_ERR_ACC = 3 };
 
@@ -256,7 +245,7 @@ k_matmul_umma(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ 
                     uint32_t ts[15];
 #pragma unroll
                     for (int s = 0; s < 15; ++s) ts[s] = t[s][q];
-                    const uint64_t v = combine15(ts);
+                    const uint64_t v = vpf::combine15(ts);
                     const int64_t c = col0 + 16 * (warp >> 2) + 4 * g + q;
                     if (r < m && c < n) C[r * n + c] = c0k == 0 ? v : vgl::add(C[r * n + c], v);
                 }
