@@ -19,6 +19,19 @@ constexpr uint64_t EPS = 0xFFFFFFFFull;   // 2^32 - 1 = 2^64 mod p
 
 __host__ __device__ __forceinline__ uint64_t pack(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
 
+// The carry-chain instructions of the ALU pipe (add.cc / addc / sub.cc / subc) have twins on the FMA pipe:
+// mad.lo.cc / madc.lo with a multiplier of 1, -1 or 0 taken from the constant bank (so that the assembler
+// keeps them multiply-adds).  With VGL_FMA_CARRY the conditional corrections of sub, reduce128 and the
+// power-of-two shifts (+-(2^32 - 1) after a borrow or carry) and the products h*(2^32 - 1) are issued that
+// way: the kernels built on these primitives are bound by the ALU pipe while the FMA pipe is a quarter busy.
+// Bits: 1 = the correction of sub, 2 = reduce128 (the tail of every full multiply), 4 = the power-of-two shifts.
+#ifndef VGL_FMA_CARRY
+#define VGL_FMA_CARRY 7
+#endif
+#ifdef __CUDACC__
+static __constant__ uint32_t VGL_ONE = 1u, VGL_M1 = 0xFFFFFFFFu, VGL_ZERO = 0u;
+#endif
+
 // ---- portable versions (host, and the oracle of the PTX versions) -----------------
 __host__ __device__ __forceinline__ uint64_t add_c(uint64_t a, uint64_t b) {
     uint64_t s = a + b;
@@ -47,6 +60,15 @@ __host__ __device__ __forceinline__ uint64_t reduce128_c(uint64_t lo, uint64_t h
 __host__ __device__ __forceinline__ uint64_t sub(uint64_t a, uint64_t b) {
 #ifdef __CUDA_ARCH__
     uint32_t d0, d1, m;
+#if VGL_FMA_CARRY & 1
+    asm("sub.cc.u32 %0, %3, %5;\n\t"
+        "subc.cc.u32 %1, %4, %6;\n\t"
+        "subc.u32 %2, 0, 0;\n\t"              // m = borrow ? 0xffffffff : 0
+        "mad.lo.cc.u32 %0, %2, %7, %0;\n\t"   // d -= borrow ? EPS : 0:  lo += m*(-1) = (borrow ? 1 : 0),
+        "madc.lo.u32 %1, %2, %8, %1;"          //                         hi += m*1 + carry = -borrow + carry
+        : "=&r"(d0), "=&r"(d1), "=&r"(m)
+        : "r"((uint32_t)a), "r"((uint32_t)(a >> 32)), "r"((uint32_t)b), "r"((uint32_t)(b >> 32)), "r"(VGL_M1), "r"(VGL_ONE));
+#else
     asm("sub.cc.u32 %0, %3, %5;\n\t"
         "subc.cc.u32 %1, %4, %6;\n\t"
         "subc.u32 %2, 0, 0;\n\t"          // m = borrow ? 0xffffffff : 0
@@ -54,6 +76,7 @@ __host__ __device__ __forceinline__ uint64_t sub(uint64_t a, uint64_t b) {
         "subc.u32 %1, %1, 0;"
         : "=&r"(d0), "=&r"(d1), "=&r"(m)
         : "r"((uint32_t)a), "r"((uint32_t)(a >> 32)), "r"((uint32_t)b), "r"((uint32_t)(b >> 32)));
+#endif
     return pack(d0, d1);
 #else
     return sub_c(a, b);
@@ -75,7 +98,30 @@ __host__ __device__ __forceinline__ uint64_t add(uint64_t a, uint64_t b) {
 
 // (hi:lo) mod p, canonical: 17 instructions on the device
 __host__ __device__ __forceinline__ uint64_t reduce128(uint64_t lo, uint64_t hi) {
-#ifdef __CUDA_ARCH__
+#if defined(__CUDA_ARCH__) && (VGL_FMA_CARRY & 2)
+    uint32_t r0, r1;
+    asm("{\n\t.reg .u32 m, c, e0, e1;\n\t.reg .b64 e;\n\t.reg .pred q;\n\t"
+        "sub.cc.u32 %0, %2, %5;\n\t"           // t = lo - hh
+        "subc.cc.u32 %1, %3, 0;\n\t"
+        "subc.u32 m, 0, 0;\n\t"
+        "mad.lo.cc.u32 %0, m, %6, %0;\n\t"     // t -= borrow ? EPS : 0   (FMA pipe, cannot borrow again)
+        "madc.lo.u32 %1, m, %7, %1;\n\t"
+        "mul.wide.u32 e, %4, %6;\n\t"          // e = hl*EPS               (FMA pipe)
+        "mov.b64 {e0, e1}, e;\n\t"
+        "add.cc.u32 %0, %0, e0;\n\t"           // r = t + e
+        "addc.cc.u32 %1, %1, e1;\n\t"
+        "addc.u32 c, 0, 0;\n\t"                // c = carry
+        "mad.lo.cc.u32 %0, c, %6, %0;\n\t"     // r += carry ? EPS : 0:  lo -= c, its carry k = no borrow,
+        "madc.lo.u32 %1, c, %8, %1;\n\t"       //                        hi += k            (cannot carry again)
+        "setp.eq.u32 q, %1, 0xffffffff;\n\t"   // r >= p  <=>  hi == 2^32-1 and lo != 0; then r - p = lo - 1
+        "setp.ne.and.u32 q, %0, 0, q;\n\t"
+        "@q mov.u32 %1, 0;\n\t"
+        "@q add.u32 %0, %0, 0xffffffff;\n\t}"
+        : "=&r"(r0), "=&r"(r1)
+        : "r"((uint32_t)lo), "r"((uint32_t)(lo >> 32)), "r"((uint32_t)hi), "r"((uint32_t)(hi >> 32)),
+          "r"(VGL_M1), "r"(VGL_ONE), "r"(VGL_ZERO));
+    return pack(r0, r1);
+#elif defined(__CUDA_ARCH__)
     uint32_t r0, r1;
     asm("{\n\t.reg .u32 m, e0, e1;\n\t.reg .pred q;\n\t"
         "sub.cc.u32 %0, %2, %5;\n\t"       // t = lo - hh
@@ -107,6 +153,22 @@ __host__ __device__ __forceinline__ uint64_t reduce128(uint64_t lo, uint64_t hi)
 // (l1:l0) + h*(2^32-1) mod p, canonical; (l1:l0) is any u64, h any u32: 12 instructions
 __device__ __forceinline__ uint64_t add_mul_eps(uint32_t l0, uint32_t l1, uint32_t h) {
     uint32_t r0, r1;
+#if VGL_FMA_CARRY & 4
+    asm("{\n\t.reg .u32 c, e0, e1;\n\t.reg .b64 e;\n\t.reg .pred q;\n\t"
+        "mul.wide.u32 e, %4, %5;\n\t"          // e = h*EPS (FMA pipe)
+        "mov.b64 {e0, e1}, e;\n\t"
+        "add.cc.u32 %0, %2, e0;\n\t"
+        "addc.cc.u32 %1, %3, e1;\n\t"
+        "addc.u32 c, 0, 0;\n\t"
+        "mad.lo.cc.u32 %0, c, %5, %0;\n\t"     // += carry ? EPS : 0 (FMA pipe)
+        "madc.lo.u32 %1, c, %6, %1;\n\t"
+        "setp.eq.u32 q, %1, 0xffffffff;\n\t"
+        "setp.ne.and.u32 q, %0, 0, q;\n\t"
+        "@q mov.u32 %1, 0;\n\t"
+        "@q add.u32 %0, %0, 0xffffffff;\n\t}"
+        : "=&r"(r0), "=&r"(r1) : "r"(l0), "r"(l1), "r"(h), "r"(VGL_M1), "r"(VGL_ZERO));
+    return pack(r0, r1);
+#endif
     asm("{\n\t.reg .u32 m, e0, e1;\n\t.reg .pred q;\n\t"
         "sub.cc.u32 e0, 0, %4;\n\t"
         "subc.u32 e1, %4, 0;\n\t"
@@ -203,11 +265,17 @@ __device__ __forceinline__ uint64_t mul_pow2(uint64_t x) {
             return reduce128(pack(0, l0), pack(l1, l2));
         } else {
             // l0 phi^2 + l1 phi^3 + l2 phi^4 = l0*(2^32-1) - (l2:l1); (l2:l1) < 2^63 is canonical
+#if VGL_FMA_CARRY & 4
+            uint64_t e;
+            asm("mul.wide.u32 %0, %1, %2;" : "=l"(e) : "r"(l0), "r"(VGL_M1));     // FMA pipe
+            return sub(e, pack(l1, l2));
+#else
             uint32_t e0, e1;
             asm("sub.cc.u32 %0, 0, %2;\n\t"
                 "subc.u32 %1, %2, 0;"
                 : "=&r"(e0), "=&r"(e1) : "r"(l0));
             return sub(pack(e0, e1), pack(l1, l2));
+#endif
         }
     }
 #else

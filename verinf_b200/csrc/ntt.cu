@@ -549,12 +549,14 @@ __device__ __forceinline__ uint64_t mul_pow2_any(uint64_t x) {
 }
 // v[j] = c[j] * w_{16*RHO}^(T*j), j < 16: the part of the coset twist that varies inside a thread's
 // first radix-16 butterfly; w_{16*RHO} is a power of two for RHO <= 4, so these are shifts.
+// The coefficients are read from the thread's own column of a shared-memory array (c[J * stride]): holding
+// them in registers across the cosets costs 32 registers and one resident CTA.
 template <int RHO, int T, int J = 0>
-__device__ __forceinline__ void coset_shift(const uint64_t (&c)[16], uint64_t (&v)[16]) {
+__device__ __forceinline__ void coset_shift(const uint64_t* __restrict__ c, int stride, uint64_t (&v)[16]) {
     if constexpr (J < 16) {
         constexpr int E = (vdft::root_exp(RHO == 4 ? 6 : RHO == 2 ? 5 : 4) * T * J) % 192;
-        v[J] = mul_pow2_any<E>(c[J]);
-        coset_shift<RHO, T, J + 1>(c, v);
+        v[J] = mul_pow2_any<E>(c[J * stride]);
+        coset_shift<RHO, T, J + 1>(c, stride, v);
     }
 }
 
@@ -641,22 +643,24 @@ __global__ void __launch_bounds__(tile_max_threads(LOGL), (LOGL >= 4 && LOGL <= 
             }
         }
     } else {
-        // c2[j] = coefficient l1 = first_pos(j) (held in c[brev(j)]) times K^-1 7^l, l = l1*n1 + l2
-        uint64_t c2[EPT];
+        // c2[j] = coefficient l1 = first_pos(j) (held in c[brev(j)]) times K^-1 7^l, l = l1*n1 + l2; kept in
+        // shared memory behind the tile, element j of thread tid at c2[j * blockDim.x + tid]
+        uint64_t* c2 = sm + (size_t)L * CP + tid;
+        const int nthr = blockDim.x;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             uint32_t l1 = SF::first_pos(j, w);
             uint64_t sc = valid ? __ldg(a.cscale + colg + n1 * l1) : 0;
-            c2[j] = mul(c[brev(j, LR)], sc);
+            c2[j * nthr] = mul(c[brev(j, LR)], sc);
         }
 #pragma unroll 1   // (fully unrolled: no spills, but 11.9 ms against 10.9 ms at K = 2^16)
         for (int t = 0; t < RHO; ++t) {
             if (SF::NS > 1) __syncthreads();   // previous coset finished reading the tile
             switch (t) {
-                case 0: coset_shift<RHO, 0>(c2, v); break;
-                case 1: coset_shift<RHO, 1>(c2, v); break;
-                case 2: coset_shift<RHO, 2 % RHO>(c2, v); break;
-                default: coset_shift<RHO, 3 % RHO>(c2, v); break;
+                case 0: coset_shift<RHO, 0>(c2, nthr, v); break;
+                case 1: coset_shift<RHO, 1>(c2, nthr, v); break;
+                case 2: coset_shift<RHO, 2 % RHO>(c2, nthr, v); break;
+                default: coset_shift<RHO, 3 % RHO>(c2, nthr, v); break;
             }
             run_stages<LOGL, false, true, 0, RHO>(v, sm, CP, col, w, a.twL, a.twRL, t);
             if (valid) {
@@ -1047,6 +1051,7 @@ int launch_pass(int logL, bool inv, int mode, PassArgs& a, int64_t items, cudaSt
 template <int LOGL, int RHO>
 int launch_mid_t(const MidArgs& a, int64_t items, cudaStream_t st) {
     size_t smem = tile_smem(LOGL, a.logC);
+    if (RHO != 0) smem += (size_t)16 * tile_threads(LOGL, a.logC) * 8;     // the scaled coefficients between the cosets
     auto fn = k_encode_mid<LOGL, RHO>;
     if (smem > 48 * 1024) VI_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int64_t grid = items * a.tiles_per_item;
