@@ -532,14 +532,18 @@ def run_native(a):
         dom_ms_per_step = dom[1][0] / a.steps
         achieved = bytes_per_step / (dom_ms_per_step * 1e-3) / 1e9 if dom_ms_per_step else 0.0
         enc_ms = sum(prof.get(t_, (0, 0))[0] for t_ in ("encode_pass1", "encode_mid", "encode_pass3")) / a.steps
-        # integer roofline of the encode: radix-16 butterfly element-stages and full modular multiplies at
-        # their ALU-pipe cost measured with the integer-pipe microbenchmark (8.8 and 17.3 ALU lane-ops), against
-        # 148 SMs x 64 ALU lanes per clock at the SM clock sampled during the run
+        # integer roofline of the encode: radix-16 butterfly element-stages and full modular multiplies at the
+        # warp-instruction counts of the field primitives measured with the integer-pipe microbenchmark
+        # (per element-stage 7.1 ALU-pipe + 4.7 FMA-pipe instructions, per multiply 15.1 + 13.8), against
+        # 148 SMs x 64 lanes per clock per pipe at the SM clock sampled during the run.  The ALU pipe is the
+        # fuller of the two; `issue_floor_ms` is the same work at the 128 lanes/clk/SM both pipes share.
         stages_per_row = (1 + a.blowup) * k * a.log_k
         muls_per_row = (1 + a.blowup) * k * 3 + a.blowup * k + k
-        alu_ops = rows * (stages_per_row * 8.8 + muls_per_row * 17.3)
+        alu_ops = rows * (stages_per_row * 7.1 + muls_per_row * 15.1)
+        all_ops = rows * (stages_per_row * 11.8 + muls_per_row * 29.3)
         sm_hz = ((clocks or {}).get("sm_mhz") or 1965.0) * 1e6
         alu_floor_ms = alu_ops / (148 * 64 * sm_hz) * 1e3
+        issue_floor_ms = all_ops / (148 * 128 * sm_hz) * 1e3
         line = {
             "metric": METRIC, "value": elems * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps,
@@ -567,6 +571,7 @@ def run_native(a):
                             "gbs_algorithmic": rows * 8 * (k + n) / (enc_ms * 1e-3) / 1e9 if enc_ms else None,
                             "frac_of_hbm": rows * 8 * (k + n) / (enc_ms * 1e-3) / 1e9 / hbm_peak if enc_ms else None},
             "int_roofline": {"bound": "integer ALU pipe (64 lanes/clk/SM)", "encode_floor_ms": alu_floor_ms,
+                             "issue_floor_ms": issue_floor_ms,
                              "encode_ms": enc_ms, "frac": alu_floor_ms / enc_ms if enc_ms else None},
             "gpu_launches": launches,
             "clocks": clocks,
@@ -655,7 +660,8 @@ def build_int_pipes():
     out = ROOT / "build" / "int_pipes"
     src = ROOT / "bench_int_pipes.cu"
     out.parent.mkdir(exist_ok=True)
-    if not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
+    deps = [src] + sorted((ROOT / "verinf_b200" / "csrc").glob("*.cuh"))
+    if not out.exists() or out.stat().st_mtime < max(d.stat().st_mtime for d in deps):
         env = {k_: v for k_, v in os.environ.items() if k_ not in ("CC", "CXX")}
         subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
                                "--expt-relaxed-constexpr", "-I", str(ROOT), "-o", str(out), str(src)], env=env)

@@ -241,6 +241,12 @@ int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, int64_t size
 int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                       int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
                       int flags, uint64_t r, uint64_t* out, void* partials, void* stream);
+/* Fills the g(1) that vi_sumcheck_run leaves out, on the device: for i = 1 .. n_rounds-1,
+ * samples[8*i + 1] = g_{i-1}(coins[i-1]) - samples[8*i], with g_{i-1} interpolated from its deg + 1
+ * samples at the nodes 0..deg (what the reference's verifier recomputes, layergkr/sumcheck.py:235-262).
+ * coins: HOST array of n_rounds canonical challenges; n_rounds <= 64, 1 <= deg <= 7.  Row 0 must be
+ * complete.  One launch of one CTA; lets the caller copy finished round polynomials in one transfer. */
+int vi_sumcheck_complete(uint64_t* samples, int n_rounds, int deg, const uint64_t* coins, void* stream);
 
 /* ---- remaining exports of the reference module (not on the hot path) -------------
  * poly_eval (prover/kernels/gl_extras.cuh:93-108), gl_matmul / gl_matvec

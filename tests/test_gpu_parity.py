@@ -527,6 +527,9 @@ def test_sumcheck_vs_oracle(logn, terms):
     got = prob2.run(coins)
     assert got == [[int(v) for v in row[:len(got[0])]] for row in samples]
     assert prob2.finals() == [int(v) for v in finals]
+    prob3 = lg.SumcheckProblem(dev(tabs), terms)          # g(1) filled on the host instead of by vi_sumcheck_complete
+    rows = lg.samples_to_host(prob3.run_device(coins), prob3.deg)
+    assert all(row[1] == 0 for row in rows[1:]) and lg.SumcheckProblem.complete_samples(rows, coins) == got
 
 
 # ---------------------------------------------------------------- misc ops ---

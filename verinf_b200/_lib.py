@@ -54,6 +54,7 @@ SIGNATURES = {
     "vi_sumcheck_claim": (_int, [_p, _i64, _int, _i64, _int, _p, _p, _p, _p, _p, _p]),
     "vi_sumcheck_run": (_int, [_p, _i64, _int, _i64, _int, _p, _p, _p, _p, _int, _p, _p, _p]),
     "vi_sumcheck_round": (_int, [_p, _i64, _int, _i64, _int, _p, _p, _p, _int, _u64, _p, _p, _p]),
+    "vi_sumcheck_complete": (_int, [_p, _int, _int, _p, _p]),
     "vi_poly_eval": (_int, [_p, _i64, _i64, _p, _i64, _p, _p]),
     "vi_gl_matmul": (_int, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "vi_gl_matmul_tc_scratch_bytes": (_i64, [_i64, _i64, _i64]),

@@ -6,9 +6,10 @@
 // 2^96 = -1 (mod p).
 //
 // The device versions are written on 32-bit limbs with explicit carry chains
-// (add.cc / subc): on sm_100a the integer ALU pipe issues half a warp per cycle and is
-// the limiter of the NTT kernels, so every op is the shortest carry-chain sequence
-// found: sub = 5 instructions, add = neg + sub = 7, reduce128 = 17.
+// (add.cc / subc): on sm_100a the integer ALU pipe and the FMA pipe each issue half a warp
+// per cycle and the NTT kernels are bound by them, so every op is the shortest sequence found
+// (sub = 5 instructions, add = neg + sub = 7, reduce128 = 16) with its instructions spread
+// over both pipes (VGL_FMA_CARRY below).
 #pragma once
 #include <cstdint>
 
@@ -77,6 +78,7 @@ __host__ __device__ __forceinline__ uint64_t sub(uint64_t a, uint64_t b) {
         : "=&r"(d0), "=&r"(d1), "=&r"(m)
         : "r"((uint32_t)a), "r"((uint32_t)(a >> 32)), "r"((uint32_t)b), "r"((uint32_t)(b >> 32)));
 #endif
+    (void)m;
     return pack(d0, d1);
 #else
     return sub_c(a, b);

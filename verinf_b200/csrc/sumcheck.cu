@@ -454,6 +454,59 @@ extern "C" int vi_sumcheck_round(uint64_t* tables, int64_t stride, int n_tables,
     return vi::check_launch("k_sumcheck<fold+round>");
 }
 
+// g_i(1) of the rounds i >= 1 of a queued run, on the device: g_i(1) = g_{i-1}(c_{i-1}) - g_i(0), with the
+// previous round polynomial evaluated from its deg + 1 samples at the nodes 0..deg by Lagrange weights.
+// The weights depend on the challenges only, so all rounds compute theirs at once (one thread per (round,
+// node)); the chain over the rounds, which needs the completed row before, is left to one warp.
+constexpr int COMPLETE_MAX_ROUNDS = 64;
+struct CompleteArgs {
+    uint64_t coin[COMPLETE_MAX_ROUNDS];      // coin[i] = challenge of round i
+    uint64_t inv_den[MAX_SAMPLES];           // 1 / prod_{j != k} (k - j)
+};
+
+__global__ void __launch_bounds__(COMPLETE_MAX_ROUNDS * MAX_SAMPLES)
+k_sumcheck_complete(uint64_t* __restrict__ samples, int n_rounds, int deg, CompleteArgs a) {
+    __shared__ uint64_t w[COMPLETE_MAX_ROUNDS][MAX_SAMPLES];
+    const int tid = threadIdx.x, rnd = tid / MAX_SAMPLES, k = tid % MAX_SAMPLES;
+    if (rnd + 1 < n_rounds && k <= deg) {           // weight of node k for the polynomial of round rnd at coin[rnd]
+        const uint64_t r = a.coin[rnd];
+        uint64_t v = a.inv_den[k];
+        for (int j = 0; j <= deg; ++j)
+            if (j != k) v = mul(v, sub(r, (uint64_t)j));
+        w[rnd][k] = v;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        for (int i = 1; i < n_rounds; ++i) {
+            uint64_t v = tid <= deg ? mul(w[i - 1][tid], samples[(int64_t)(i - 1) * 8 + tid]) : 0;
+#pragma unroll
+            for (int o = 4; o; o >>= 1) v = add(v, __shfl_xor_sync(0xffffffffu, v, o));   // MAX_SAMPLES = 8 lanes
+            if (tid == 0) samples[(int64_t)i * 8 + 1] = sub(v, samples[(int64_t)i * 8]);
+            __syncwarp();
+        }
+    }
+}
+
+extern "C" int vi_sumcheck_complete(uint64_t* samples, int n_rounds, int deg, const uint64_t* coins, void* stream) {
+    VI_REQUIRE(n_rounds >= 0 && n_rounds <= COMPLETE_MAX_ROUNDS, "sumcheck_complete: at most 64 rounds");
+    VI_REQUIRE(deg >= 1 && deg < MAX_SAMPLES, "sumcheck_complete: degree out of range");
+    if (n_rounds < 2) return VI_OK;
+    VI_REQUIRE(samples && coins, "sumcheck_complete: null pointer");
+    CompleteArgs a{};
+    for (int i = 0; i + 1 < n_rounds; ++i) {
+        VI_REQUIRE(coins[i] < vgl::P, "sumcheck_complete: challenge not canonical");
+        a.coin[i] = coins[i];
+    }
+    for (int k = 0; k <= deg; ++k) {
+        uint64_t den = 1;
+        for (int j = 0; j <= deg; ++j)
+            if (j != k) den = vgl::hmul(den, j < k ? (uint64_t)(k - j) : vgl::P - (uint64_t)(j - k));
+        a.inv_den[k] = vgl::hpow(den, vgl::P - 2);
+    }
+    k_sumcheck_complete<<<1, COMPLETE_MAX_ROUNDS * MAX_SAMPLES, 0, (cudaStream_t)stream>>>(samples, n_rounds, deg, a);
+    return vi::check_launch("k_sumcheck_complete");
+}
+
 extern "C" int vi_sumcheck_run(uint64_t* tables, int64_t stride, int n_tables, int64_t size,
                                int n_terms, const uint64_t* coefs, const int32_t* nfac, const int32_t* fac,
                                const uint64_t* coins, int n_rounds, uint64_t* samples, void* partials, void* stream) {

@@ -139,6 +139,12 @@ def _limbs(t_u64: torch.Tensor) -> torch.Tensor:
     return torch.stack([x & 0xFFFFFFFF, (x >> 32) & 0xFFFFFFFF], dim=-1)
 
 
+def samples_to_host(buf: torch.Tensor, deg: int) -> List[List[int]]:
+    """(n_rounds, 8) uint64 samples -> [[g(0..deg)] per round] as Python ints, one copy."""
+    import numpy as np
+    return buf.view(torch.int64).cpu().numpy().view(np.uint64)[:, :deg + 1].tolist()
+
+
 def _from_limbs(rows) -> List[int]:
     """[(sum of lo limbs, sum of hi limbs)] -> field elements"""
     return [(int(lo) + (int(hi) << 32)) % P for lo, hi in rows]
@@ -263,8 +269,7 @@ def _prove_sharded_queued(local_problem, make_problem, coins, local_rounds, n_ro
         rows += [_from_limbs(r) for r in red.cpu().tolist()]
     n_local = len(rows)
     if tail_buf is not None:
-        host = tail_buf.view(torch.int64).cpu().view(torch.uint64)
-        rows += [[int(v) for v in row[:deg + 1].tolist()] for row in host]
+        rows += samples_to_host(tail_buf, deg)
     out = type(local_problem).complete_samples(rows[:n_local], coins[:n_local])
     if tail_buf is not None:       # the first tail round is evaluated in full; later ones follow from their predecessor
         out += type(local_problem).complete_samples(rows[n_local:], coins[n_local:])

@@ -226,14 +226,22 @@ class SumcheckProblem:
         round, one D2H copy of all samples at the end.  Returns [[g(0..deg)] per round]."""
         n_rounds = len(coins)
         buf = self.run_device(coins)
-        host = buf.view(torch.int64).cpu().view(torch.uint64)
-        rows = [[int(v) for v in row[:self.deg + 1].tolist()] for row in host[:n_rounds]]
-        out = self.complete_samples(rows, coins)
+        if n_rounds > 1:        # g(1) of the later rounds on the device too: the host only converts
+            cs = np.array([int(c) % P for c in coins], dtype=np.uint64)
+            with torch.cuda.device(self.tables.device):
+                check(LIB.vi_sumcheck_complete(ptr(buf), n_rounds, self.deg, cs.ctypes.data, stream_ptr()))
+        out = samples_to_host(buf, self.deg)
         self._prev = out[-1] if out else None
         return out
 
     def finals(self) -> List[int]:
         return [int(v) for v in self.tables[:, 0].cpu().tolist()]
+
+
+def samples_to_host(buf: torch.Tensor, deg: int) -> List[List[int]]:
+    """(n_rounds, 8) uint64 device samples -> [[g(0..deg)] per round] as Python ints, one copy."""
+    host = buf.view(torch.int64).cpu().numpy().view(np.uint64)
+    return host[:, :deg + 1].tolist()
 
 
 _INV_DEN = {}     # n -> [1 / prod_{j != i} (i - j) mod p for i < n]  (Lagrange weights of the nodes 0..n-1)
