@@ -503,6 +503,9 @@ def test_sumcheck_masked_golden(golden, name):
     assert claim == int(g[f"{name}_claim"][0])
     assert [[y for _, y in rp] for rp in polys] == [[int(v) for v in row] for row in g[f"{name}_polys"]]
     assert chals == coins and mu == int(g[f"{name}_final_mask"][0])
+    # the same proof with every round queued (challenges drawn before the first round), masks applied afterwards
+    again = lg.prove_terms_gpu(terms, lambda i: coins[i], P, _mask_fn(tape), mu0, predraw=True)
+    assert again == (claim, polys, chals, mu)
 
 
 @pytest.mark.parametrize("logn,terms", [(12, [(1, [0, 1, 2])]), (16, [(1, [0, 1, 2])]), (13, [(3, [0, 1]), (P - 1, [2])]),

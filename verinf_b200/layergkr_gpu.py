@@ -281,14 +281,19 @@ def _poly_eval(coeffs, x, p):
 
 
 def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=None, mu0: int = 0,
-                    coins: Optional[Sequence[int]] = None):
+                    coins: Optional[Sequence[int]] = None, predraw: bool = False):
     """Sumcheck prover for sum_x sum_k c_k prod_j f_kj(x): returns
     (claim, round_polys [[(x, y), ...] per round], challenges, final_mask).
 
     `terms` is [(coef, [factor, ...])] where a factor is a Python sequence or a 1-D uint64
     CUDA tensor; factors that are the same object share one device table.  When the challenges are
     known up front pass them as `coins` (then `coin` is not called): all rounds are queued without a
-    host round trip."""
+    host round trip.  `predraw=True` does the same by calling coin(0), ..., coin(n_rounds - 1) before
+    the first round; valid when `coin` depends on the round index alone, which the reference's
+    interface implies (the callback receives nothing else, layergkr/gpu.py:402) and its call sites do
+    (layergkr/relations.py:122-123 draws all challenges from the transcript, then passes
+    `lambda i: coins[i]`).  The mask of a zero-knowledge proof only touches the scalar samples
+    (layergkr/gpu.py:392-396), so masked proofs are queued too."""
     assert field_p == P
     uniq, index, plan = [], {}, []
     for c, fs in terms:
@@ -312,11 +317,19 @@ def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=No
     deg = prob.deg
     mu = mu0 % P
     round_polys, challenges = [], []
-    if coins is not None and mask is None and n_rounds > 0:
+    if coins is None and predraw:
+        coins = [coin(rnd) for rnd in range(n_rounds)]
+    if coins is not None and n_rounds > 0:
         challenges = [int(c) % P for c in coins]
         all_ys = prob.run(challenges)
         claim = (all_ys[0][0] + all_ys[0][1] + mu) % P       # the sum over the hypercube is g_0(0) + g_0(1)
-        round_polys = [list(enumerate(ys)) for ys in all_ys]
+        for ys, r in zip(all_ys, challenges):
+            samples = list(enumerate(ys))
+            if mask is not None:
+                h = mask(deg, mu)
+                samples = [(x, (y + _poly_eval(h, x, P)) % P) for x, y in samples]
+                mu = _poly_eval(h, r, P)
+            round_polys.append(samples)
         return claim, round_polys, challenges, mu
     claim = (prob.claim() + mu) % P
     r = None

@@ -34,6 +34,11 @@ def install_layergkr() -> None:
     reference's: they look the routines up in `layergkr.gpu` by name."""
     import importlib
     from . import layergkr_gpu
+    import functools
     gpu = importlib.import_module("layergkr.gpu")
     for name in _LAYERGKR_FAST:
         setattr(gpu, name, getattr(layergkr_gpu, name))
+    # every sumcheck call site of the reference draws its challenges before the sumcheck starts and hands
+    # over `lambda i: coins[i]` (layergkr/relations.py:122-123, layergkr/sumcheck.py:146), so the rounds can
+    # be queued without a host round trip each
+    gpu.prove_terms_gpu = functools.partial(layergkr_gpu.prove_terms_gpu, predraw=True)
