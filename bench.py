@@ -544,6 +544,11 @@ def run_native(a):
         sm_hz = ((clocks or {}).get("sm_mhz") or 1965.0) * 1e6
         alu_floor_ms = alu_ops / (148 * 64 * sm_hz) * 1e3
         issue_floor_ms = all_ops / (148 * 128 * sm_hz) * 1e3
+        # the two-term roofline the path's target is stated in: the slower of the bytes at the HBM peak and the
+        # full modular multiplies at the measured multiply rate (855 G/s at 1965 MHz, integer-pipe microbenchmark);
+        # butterflies, which are most of the work, are in neither term
+        modmul_ms = rows * muls_per_row / (855e9 * sm_hz / 1965e6) * 1e3
+        bytes_ms = rows * 8 * (k + n) / (hbm_peak * 1e9) * 1e3
         line = {
             "metric": METRIC, "value": elems * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps,
@@ -572,6 +577,8 @@ def run_native(a):
                             "frac_of_hbm": rows * 8 * (k + n) / (enc_ms * 1e-3) / 1e9 / hbm_peak if enc_ms else None},
             "int_roofline": {"bound": "integer ALU pipe (64 lanes/clk/SM)", "encode_floor_ms": alu_floor_ms,
                              "issue_floor_ms": issue_floor_ms,
+                             "bytes_or_modmul_floor_ms": max(modmul_ms, bytes_ms), "modmul_floor_ms": modmul_ms,
+                             "frac_of_bytes_or_modmul_floor": max(modmul_ms, bytes_ms) / enc_ms if enc_ms else None,
                              "encode_ms": enc_ms, "frac": alu_floor_ms / enc_ms if enc_ms else None},
             "gpu_launches": launches,
             "clocks": clocks,
