@@ -1,8 +1,7 @@
 """Stages the reference's own Python callers and CUDA headers for runs on a GPU machine.
 
 The reference tree is read-only and exists only where this project is built, so the files its
-callers need (prover/*.py, prover/ref, prover/kernels, the three test modules that pin this
-path, and layergkr with its tests) are copied unmodified into baseline/_ref/, which version
+callers need (prover/*.py, prover/ref, prover/kernels, prover/tests, and layergkr with its tests) are copied unmodified into baseline/_ref/, which version
 control ignores.  tests/test_reference_callers.py and `bench.py --extra` then run the
 reference's own call stacks from there -- once on this library through verinf_b200.shim, once
 on the reference's own JIT-built kernels -- and skip when the directory is absent.
@@ -24,10 +23,10 @@ WANTED = [
     ("prover/kernels", "*.cuh"),
     ("layergkr", "*.py"),
     ("layergkr/tests", "*.py"),
+    ("prover/tests", "*.py"),
+    ("prover/tests/vectors", "*.json"),
 ]
 WANTED_FILES = [
-    "prover/tests/test_cuda_primitives.py",
-    "prover/tests/test_persistent_weights.py",
     "LICENSE",
 ]
 

@@ -9,6 +9,11 @@ runs a job in a fresh process with `cuda_primitives` / `kquant_cuda` bound eithe
     test_commit_phase_integration), prover/tests/test_persistent_weights.py:33-80 (core.commit_weights
     determinism under the fixed MASTER_SEED) and layergkr/tests/test_gpu.py:34-115 (GPU == CPU backend
     gates) must pass on the shim;
+  * the prover tests that end in the Rust verifier (prover/tests/test_claims.py, test_routing_claim.py,
+    test_fiat_shamir.py, ... through prover/tests/_rust_verify.py) are run with a stand-in that records the
+    SHA-256 of every proof file the reference's own writer (prover/proof_dump.py) dumps: the flat test
+    prover and the production streaming prover (tape.prove -> core.prove_streaming) must dump the same
+    bytes on both backends, with the per-proof secrets fixed;
   * core.commit_weights (prover/core.py:874-910), encode_messages / hash_columns_streamed /
     merkle_build_blake3 at ELL=8192, K=16384, N=65536, and layergkr's sumcheck must give the same
     bytes on both backends (the reference's kernels are the second, independent witness).
@@ -70,7 +75,9 @@ def shim(job: str, backend: str = "shim") -> dict:
 
 
 @pytest.mark.parametrize("module,min_tests", [("test_cuda_primitives", 25), ("test_persistent_weights", 3),
-                                              ("test_gpu", 6)])
+                                              ("test_gpu", 6), ("test_gather_rows", 9),
+                                              ("test_iter_message_chunks", 15), ("test_opening_ledger", 6),
+                                              ("test_pkt_range", 13), ("test_quad_eval_accumulator", 1)])
 def test_reference_test_module_passes_on_shim(module, min_tests):
     res = shim(f"tests:{module}")
     assert not res["failed"], "\n".join(f"{k}:\n{v}" for k, v in res["failed"].items())
@@ -103,3 +110,37 @@ def test_sumcheck_transcript_equals_reference_kernels():
     assert ours["transcript_sha256"] == fused["transcript_sha256"] and ours["claim"] == fused["claim"]
     ref = reference_or_skip("sumcheck")
     assert ours["transcript_sha256"] == ref["transcript_sha256"] and ours["claim"] == ref["claim"]
+
+
+PROOF_MODULES = ["test_claims", "test_routing_claim", "test_fiat_shamir", "test_persistent_weights_link",
+                 "test_persistent_weights_p3", "test_persistent_weights_p5", "test_phase3_block", "test_reveal",
+                 "test_concat_claim", "test_rescale_claim", "test_routed_projected", "test_rmsnorm_bracket",
+                 "test_shard_streaming", "test_moe_routed", "test_empty_root_sentinel"]
+
+
+def test_dumped_proofs_byte_identical_to_reference_kernels():
+    """Every proof the reference's prover tests dump for the Rust verifier (75 proofs: honest cases,
+    cheating provers, Fiat-Shamir, persistent-weight linking, phase-3 blocks, routed MoE projections) has
+    the same SHA-256 whether the primitives underneath are this library's or the reference's own kernels,
+    and every test ends the same way on both (no Rust verifier here: honest cases stop at `assert acc`)."""
+    from concurrent.futures import ThreadPoolExecutor
+    reference_or_skip("kernels")                       # builds the reference's extension once, or skips
+    jobs = [(b, f"proofs:{m}") for m in PROOF_MODULES for b in ("shim", "reference")]
+    with ThreadPoolExecutor(max_workers=6) as pool:
+        list(pool.map(lambda bj: run_job(bj[0], bj[1], timeout=1500), jobs))
+    n_proofs, summary = 0, {}
+    for m in PROOF_MODULES:
+        ours, ref = shim(f"proofs:{m}"), reference_or_skip(f"proofs:{m}")
+        assert ours["tests"].keys() == ref["tests"].keys() and ours["tests"], m
+        for name, t in ours["tests"].items():
+            r = ref["tests"][name]
+            assert t["proofs"] == r["proofs"], (m, name, t["proofs"], r["proofs"])
+            assert t["status"][:60] == r["status"][:60], (m, name, t["status"], r["status"])
+            assert not t["status"].startswith("error"), (m, name, t["status"])
+            n_proofs += len(t["proofs"])
+        summary[m] = {"tests": len(ours["tests"]), "proofs": sum(len(t["proofs"]) for t in ours["tests"].values())}
+    assert n_proofs >= 70, summary
+    try:
+        (OUT / "refrun_proofs_summary.json").write_text(json.dumps({"identical_proofs": n_proofs, "modules": summary}, indent=1))
+    except OSError:
+        pass
