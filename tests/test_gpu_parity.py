@@ -535,6 +535,24 @@ def test_sumcheck_vs_oracle(logn, terms):
     assert all(row[1] == 0 for row in rows[1:]) and lg.SumcheckProblem.complete_samples(rows, coins) == got
 
 
+@pytest.mark.parametrize("logn,nt,nterms,predraw", [(9, 12, 20, False), (11, 30, 41, True), (7, 9, 3, True)])
+def test_sumcheck_many_tables_and_terms_vs_oracle(logn, nt, nterms, predraw):
+    """More tables / terms than one launch takes (a layer's gate batch, layergkr/relations.py:103-124): the terms
+    are split into groups, mixed degrees are extended to the common sample count, samples are added."""
+    from verinf_b200 import layergkr_gpu as lg
+    rng = np.random.default_rng(100 * logn + nt)
+    tabs = rnd_field(rng, (nt, 1 << logn))
+    terms = [(int(rng.integers(1, 1 << 40)), [int(x) for x in rng.integers(0, nt, size=int(rng.integers(1, 5)))])
+             for _ in range(nterms)]
+    terms[0] = (P - 3, [0, 1, 2, 3])                      # at least one term of full degree
+    coins = [int(c) for c in rnd_field(rng, logn)]
+    claim, samples, _ = oracle.sumcheck(tabs, terms, coins)
+    dts = [dev(t) for t in tabs]
+    got = lg.prove_terms_gpu([(c, [dts[i] for i in idx]) for c, idx in terms], lambda i: coins[i], P, predraw=predraw)
+    assert got[0] == claim and got[2] == coins
+    assert [[y for _, y in rp] for rp in got[1]] == [[int(v) for v in row[:5]] for row in samples]
+
+
 # ---------------------------------------------------------------- misc ops ---
 def test_linear_algebra(cp):
     rng = np.random.default_rng(5)

@@ -7,8 +7,8 @@ runs a job in a fresh process with `cuda_primitives` / `kquant_cuda` bound eithe
 
   * prover/tests/test_cuda_primitives.py:75-453 (25 acceptance tests, production geometry, ends in
     test_commit_phase_integration), prover/tests/test_persistent_weights.py:33-80 (core.commit_weights
-    determinism under the fixed MASTER_SEED) and layergkr/tests/test_gpu.py:34-115 (GPU == CPU backend
-    gates) must pass on the shim;
+    determinism under the fixed MASTER_SEED), layergkr/tests/test_gpu.py:34-115 (GPU == CPU backend
+    gates) and the other test modules listed below must pass on the shim;
   * the prover tests that end in the Rust verifier (prover/tests/test_claims.py, test_routing_claim.py,
     test_fiat_shamir.py, ... through prover/tests/_rust_verify.py) are run with a stand-in that records the
     SHA-256 of every proof file the reference's own writer (prover/proof_dump.py) dumps: the flat test
@@ -84,10 +84,16 @@ def test_reference_test_module_passes_on_shim(module, min_tests):
     assert len(res["passed"]) >= min_tests, res["passed"]
 
 
-def test_layergkr_gates_pass_with_fused_routines():
-    res = shim("tests:test_gpu", backend="shim+layergkr")
+@pytest.mark.parametrize("module,min_tests", [("test_gpu", 6), ("test_rs", 4), ("test_sumcheck", 11), ("test_layer", 8),
+                                              ("test_full_layer", 17), ("test_moe", 13), ("test_logup", 12),
+                                              ("test_projection", 13)])
+def test_layergkr_test_module_passes_with_fused_routines(module, min_tests):
+    """layergkr's own tests with this package's encode / commit / sumcheck routines set on layergkr.gpu
+    (shim.install_layergkr): the layer provers of full_layer.py, layer.py and moe.py reach them through
+    rs.py and sumcheck.py; test_full_layer's gate batch has hundreds of tables in one sumcheck."""
+    res = shim(f"tests:{module}", backend="shim+layergkr")
     assert not res["failed"], "\n".join(f"{k}:\n{v}" for k, v in res["failed"].items())
-    assert len(res["passed"]) >= 6
+    assert len(res["passed"]) >= min_tests, res["passed"]
 
 
 def test_commit_weights_root_equals_reference_kernels():

@@ -238,6 +238,56 @@ class SumcheckProblem:
         return [int(v) for v in self.tables[:, 0].cpu().tolist()]
 
 
+_MAX_TABLES, _MAX_TERMS = 8, 8          # per launch of the sumcheck kernels (csrc/sumcheck.cu)
+
+
+class TermGroups:
+    """A sum of products with more tables or terms than one kernel launch takes (a layer's gate batch,
+    layergkr/relations.py:103-124, has hundreds): the sum is linear in its terms, so the terms are split
+    into groups that fit, every group is its own SumcheckProblem folded with the same challenges, and the
+    round samples are added.  A group of lower degree is extended to the common number of samples by
+    evaluating its round polynomial at the further nodes.  Same interface as SumcheckProblem."""
+
+    def __init__(self, rows: Sequence[torch.Tensor], plan: Sequence):
+        self.deg = max(len(idx) for _, idx in plan)
+        groups, cur, used = [], [], set()
+        for c, idx in plan:
+            if cur and (len(cur) == _MAX_TERMS or len(used | set(idx)) > _MAX_TABLES):
+                groups.append(cur)
+                cur, used = [], set()
+            cur.append((c, idx))
+            used |= set(idx)
+        groups.append(cur)
+        self.problems = []
+        for g in groups:
+            need = sorted({i for _, idx in g for i in idx})
+            at = {t: j for j, t in enumerate(need)}
+            tables = torch.stack([rows[t].view(torch.int64) for t in need]).view(torch.uint64).contiguous()
+            self.problems.append(SumcheckProblem(tables, [(c, [at[i] for i in idx]) for c, idx in g]))
+        self.size = self.problems[0].size
+
+    def _add(self, per_group: Sequence[List[int]]) -> List[int]:
+        n = self.deg + 1
+        out = [0] * n
+        for ys in per_group:
+            ys = list(ys) + [_interp_at(ys, x) for x in range(len(ys), n)]
+            out = [(a + b) % P for a, b in zip(out, ys)]
+        return out
+
+    def claim(self) -> int:
+        return sum(p.claim() for p in self.problems) % P
+
+    def round(self, r: Optional[int]) -> Optional[List[int]]:
+        res = [p.round(r) for p in self.problems]
+        self.size = self.problems[0].size
+        return None if res[0] is None else self._add(res)
+
+    def run(self, coins: Sequence[int]) -> List[List[int]]:
+        per = [p.run(coins) for p in self.problems]
+        self.size = 1
+        return [self._add([g[i] for g in per]) for i in range(len(coins))]
+
+
 def samples_to_host(buf: torch.Tensor, deg: int) -> List[List[int]]:
     """(n_rounds, 8) uint64 device samples -> [[g(0..deg)] per round] as Python ints, one copy."""
     host = buf.view(torch.int64).cpu().numpy().view(np.uint64)
@@ -311,8 +361,11 @@ def prove_terms_gpu(terms, coin: Callable[[int], int], field_p: int = P, mask=No
             rows.append(f.to(device="cuda").reshape(-1))
         else:
             rows.append(torch.tensor([int(x) % P for x in f], dtype=torch.uint64, device="cuda"))
-    tables = torch.stack([r.view(torch.int64) for r in rows]).view(torch.uint64).contiguous()
-    prob = SumcheckProblem(tables, plan)
+    if len(rows) > _MAX_TABLES or len(plan) > _MAX_TERMS:
+        prob = TermGroups(rows, plan)
+    else:
+        tables = torch.stack([r.view(torch.int64) for r in rows]).view(torch.uint64).contiguous()
+        prob = SumcheckProblem(tables, plan)
     n_rounds = prob.size.bit_length() - 1
     deg = prob.deg
     mu = mu0 % P
