@@ -1,7 +1,7 @@
 """Stages the reference's own Python callers and CUDA headers for runs on a GPU machine.
 
 The reference tree is read-only and exists only where this project is built, so the files its
-callers need (prover/*.py, prover/ref, prover/kernels, prover/tests, and layergkr with its tests) are copied unmodified into baseline/_ref/, which version
+callers need (prover/*.py, prover/ref, prover/kernels, prover/tests, demo, and layergkr with its tests) are copied unmodified into baseline/_ref/, which version
 control ignores.  tests/test_reference_callers.py and `bench.py --extra` then run the
 reference's own call stacks from there -- once on this library through verinf_b200.shim, once
 on the reference's own JIT-built kernels -- and skip when the directory is absent.
@@ -25,6 +25,8 @@ WANTED = [
     ("layergkr/tests", "*.py"),
     ("prover/tests", "*.py"),
     ("prover/tests/vectors", "*.json"),
+    ("demo", "*.py"),
+    ("demo", "*.txt"),
 ]
 WANTED_FILES = [
     "LICENSE",

@@ -16,6 +16,7 @@ Jobs
                    every test_* function, as the reference's run_tests.py does
   proofs:<module>  the same, for modules whose tests end in the Rust verifier: a stand-in records the
                    SHA-256 of every dumped proof file instead (see job_proofs)
+  demo:<name>      demo/demo_<name>.py (llama7b): a whole transformer block proved and dumped; digest of the file
   commit_weights   core.commit_weights (prover/core.py:874-910) of a small seeded tape at the
                    production geometry: root and a digest of every Merkle level
   kernels          encode_messages + hash_columns_streamed + merkle_build_blake3 at
@@ -97,9 +98,15 @@ def job_proofs(modname: str) -> dict:
                     'exit 3\n')
     stub.chmod(stub.stat().st_mode | stat.S_IXUSR)
     os.environ["LIGERO_VERIFY_PROOF"] = str(stub)
-    # The production prover pads and blinds under a fresh secret per proof (core.new_zk_seed ->
-    # secrets.token_bytes, prover/core.py:3265-3275), so two runs never dump the same bytes.  For the
-    # comparison the source of those secrets is replaced by a counter-keyed hash, the same in both processes.
+    _fix_secrets()
+    out = job_tests_with(modname, log)
+    return out
+
+
+def _fix_secrets() -> None:
+    """The production prover pads and blinds under a fresh secret per proof (core.new_zk_seed ->
+    secrets.token_bytes, prover/core.py:3265-3275), so two runs never dump the same bytes.  For a
+    comparison the source of those secrets is replaced by a counter-keyed hash, the same in both processes."""
     import secrets
     ctr = [0]
 
@@ -107,8 +114,46 @@ def job_proofs(modname: str) -> dict:
         ctr[0] += 1
         return hashlib.sha256(b"verinf_b200 proofs job " + str(ctr[0]).encode()).digest()[:n]
     secrets.token_bytes = fixed_token_bytes
-    out = job_tests_with(modname, log)
-    return out
+
+
+def job_demo(name: str) -> dict:
+    """demo/demo_<name>.py main() without a checkpoint: one transformer block of the demo's architecture
+    (demo_llama7b: d = 4096, d_ff = 11008, SEQ = 2 at ELL=8192/K=16384/N=65536; RmsNorm, Q/K/V/O and FFN
+    matmuls, RoPE, softmax, SiLU, Hadamard, residual adds) with seeded random weights, proved by tape.prove
+    and dumped by the reference's proof writer; digest and size of the dumped file.  LIGERO_T_QUERIES
+    (default here 4) sets the number of opened columns, which only sizes the dump."""
+    import os
+    import tempfile
+    os.environ.setdefault("LIGERO_T_QUERIES", "4")
+    import torch
+    _fix_secrets()
+    torch.manual_seed(20240611)
+    torch.cuda.manual_seed_all(20240611)
+    sys.path.insert(0, str(REF / "demo"))
+    demo = importlib.import_module(f"demo_{name}")
+    fd, path = tempfile.mkstemp(suffix=".json")
+    os.close(fd)
+    import contextlib
+    import io
+    import re
+    torch.cuda.synchronize()
+    t0 = time.time()
+    log = io.StringIO()
+    try:
+        with contextlib.redirect_stdout(log):
+            demo.main(dump_proof=path, with_lm_head=False, engine=True)
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+        h, nbytes = hashlib.sha256(), 0
+        with open(path, "rb") as f:
+            for blk in iter(lambda: f.read(1 << 24), b""):
+                h.update(blk)
+                nbytes += len(blk)
+    finally:
+        os.unlink(path)
+    m = re.findall(r"prove:\s+([0-9.]+)s", log.getvalue())       # the demo's own timer around tape.prove
+    return {"demo": name, "proof_sha256": h.hexdigest(), "proof_bytes": nbytes, "s": dt,
+            "prove_s": float(m[-1]) if m else None, "peak_gb": torch.cuda.max_memory_allocated() / 1e9}
 
 
 def job_tests_with(modname: str, log: Path) -> dict:
@@ -235,6 +280,8 @@ def main() -> None:
             out.update(job_tests(a.job.split(":", 1)[1]))
         elif a.job.startswith("proofs:"):
             out.update(job_proofs(a.job.split(":", 1)[1]))
+        elif a.job.startswith("demo:"):
+            out.update(job_demo(a.job.split(":", 1)[1]))
         elif a.job == "commit_weights":
             out.update(job_commit_weights())
         elif a.job == "kernels":

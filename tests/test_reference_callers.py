@@ -150,3 +150,17 @@ def test_dumped_proofs_byte_identical_to_reference_kernels():
         (OUT / "refrun_proofs_summary.json").write_text(json.dumps({"identical_proofs": n_proofs, "modules": summary}, indent=1))
     except OSError:
         pass
+
+
+def test_llama7b_block_proof_byte_identical_to_reference_kernels():
+    """demo/demo_llama7b.py, the reference's production driver, without a checkpoint: one Llama-2-7B-shaped
+    block (d = 4096, d_ff = 11008, SEQ = 2, seeded random weights) at ELL=8192/K=16384/N=65536, committed and
+    proved by the streaming prover and dumped by the reference's proof writer.  The 6 MB proof file has the
+    same SHA-256 on this library and on the reference's own kernels."""
+    from concurrent.futures import ThreadPoolExecutor
+    reference_or_skip("kernels")
+    with ThreadPoolExecutor(max_workers=2) as pool:
+        list(pool.map(lambda b: run_job(b, "demo:llama7b", timeout=1500), ("shim", "reference")))
+    ours, ref = shim("demo:llama7b"), reference_or_skip("demo:llama7b")
+    assert ours["proof_bytes"] == ref["proof_bytes"] > 1 << 20
+    assert ours["proof_sha256"] == ref["proof_sha256"]
