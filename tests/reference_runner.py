@@ -17,6 +17,7 @@ Jobs
   proofs:<module>  the same, for modules whose tests end in the Rust verifier: a stand-in records the
                    SHA-256 of every dumped proof file instead (see job_proofs)
   demo:<name>      demo/demo_<name>.py (llama7b): a whole transformer block proved and dumped; digest of the file
+  kquant           kquant_cuda.kquant_to_field against gguf-py's dequantize -> quantize_to_field on seeded blocks
   commit_weights   core.commit_weights (prover/core.py:874-910) of a small seeded tape at the
                    production geometry: root and a digest of every Merkle level
   kernels          encode_messages + hash_columns_streamed + merkle_build_blake3 at
@@ -156,6 +157,31 @@ def job_demo(name: str) -> dict:
             "prove_s": float(m[-1]) if m else None, "peak_gb": torch.cuda.max_memory_allocated() / 1e9}
 
 
+def job_kquant() -> dict:
+    """The gate of prover/tests/test_kquant_kernel.py:31-62 on seeded synthetic super-blocks (that test needs a
+    real GGUF file): kquant_to_field of Q4_K / Q5_K / Q6_K bytes against gguf.quants.dequantize ->
+    loader.quantize_to_field, 4096 blocks per type, scales drawn as finite fp16 values of mixed magnitude."""
+    import numpy as np
+    import torch
+    from gguf import GGMLQuantizationType
+    from gguf.quants import dequantize
+    from kquant_cuda import kquant_to_field
+    from loader import quantize_to_field
+    S = 1 << 12
+    out = {}
+    for qt, nbytes, scale_at in (("Q4_K", 144, (0, 2)), ("Q5_K", 176, (0, 2)), ("Q6_K", 210, (208,))):
+        rng = np.random.default_rng(len(qt) * 1000 + nbytes)
+        raw = rng.integers(0, 256, (4096, nbytes), dtype=np.uint8)
+        for off in scale_at:                     # d / dmin: finite halves between 2^-14 and 2^2, either sign
+            h = (rng.uniform(-1, 1, 4096) * np.exp2(rng.integers(-14, 3, 4096))).astype(np.float16)
+            raw[:, off:off + 2] = h.view(np.uint8).reshape(4096, 2)
+        ref = quantize_to_field(torch.from_numpy(dequantize(raw, GGMLQuantizationType[qt]).copy()), S).reshape(-1)
+        got = kquant_to_field(torch.from_numpy(raw).cuda(), qt, S)
+        out[qt] = {"equals_gguf_numpy": bool(torch.equal(ref.view(torch.int64), got.view(torch.int64))),
+                   "sha256": _sha(got), "n": int(got.numel())}
+    return {"kquant": out}
+
+
 def job_tests_with(modname: str, log: Path) -> dict:
     path = next((d for d in (REF / "prover" / "tests", REF / "layergkr" / "tests") if (d / f"{modname}.py").exists()), None)
     if path is None:
@@ -282,6 +308,8 @@ def main() -> None:
             out.update(job_proofs(a.job.split(":", 1)[1]))
         elif a.job.startswith("demo:"):
             out.update(job_demo(a.job.split(":", 1)[1]))
+        elif a.job == "kquant":
+            out.update(job_kquant())
         elif a.job == "commit_weights":
             out.update(job_commit_weights())
         elif a.job == "kernels":

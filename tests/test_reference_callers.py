@@ -164,3 +164,12 @@ def test_llama7b_block_proof_byte_identical_to_reference_kernels():
     ours, ref = shim("demo:llama7b"), reference_or_skip("demo:llama7b")
     assert ours["proof_bytes"] == ref["proof_bytes"] > 1 << 20
     assert ours["proof_sha256"] == ref["proof_sha256"]
+
+
+def test_kquant_lift_equals_reference_kernel_and_gguf():
+    """prover/tests/test_kquant_kernel.py's gate on synthetic super-blocks: both kernels equal
+    gguf.quants.dequantize -> loader.quantize_to_field, and each other, for Q4_K, Q5_K, Q6_K."""
+    ours, ref = shim("kquant"), reference_or_skip("kquant")
+    for qt in ("Q4_K", "Q5_K", "Q6_K"):
+        assert ours["kquant"][qt]["equals_gguf_numpy"] and ref["kquant"][qt]["equals_gguf_numpy"], qt
+        assert ours["kquant"][qt]["sha256"] == ref["kquant"][qt]["sha256"], qt
