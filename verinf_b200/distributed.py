@@ -253,6 +253,27 @@ def prove_terms_sharded(local_problem, make_problem: Callable, coin: Callable[[i
     return claim, polys, chals
 
 
+def _complete_on_device(rows: torch.Tensor, deg: int, coins: Sequence[int]) -> None:
+    """g(1) of rows 1.. of an (n, 8) uint64 CUDA sample buffer, in place (vi_sumcheck_complete)."""
+    import numpy as np
+    from ._lib import LIB, check, ptr, stream_ptr
+    if rows.size(0) < 2:
+        return
+    cs = np.array([int(c) % P for c in coins[:rows.size(0)]], dtype=np.uint64)
+    with torch.cuda.device(rows.device):
+        check(LIB.vi_sumcheck_complete(ptr(rows), rows.size(0), deg, cs.ctypes.data, stream_ptr()))
+
+
+def _limbs_to_field_device(limbs: torch.Tensor) -> torch.Tensor:
+    """(..., 2) int64 limb sums on a CUDA device -> (...) canonical uint64: lo + hi * 2^32 mod p with the
+    library's field kernels (both sums stay below 2^63 < p for up to 2^31 ranks)."""
+    from . import cuda_primitives as cp
+    lo = limbs[..., 0].contiguous().view(torch.uint64)
+    hi = limbs[..., 1].contiguous().view(torch.uint64)
+    two32 = torch.full(hi.shape, 1 << 32, dtype=torch.int64, device=hi.device).view(torch.uint64)
+    return cp.gl_add(lo, cp.gl_mul(hi, two32))
+
+
 def _prove_sharded_queued(local_problem, make_problem, coins, local_rounds, n_rounds, world, group):
     """prove_terms_sharded with the challenges known up front; see there."""
     deg = local_problem.deg
@@ -264,15 +285,31 @@ def _prove_sharded_queued(local_problem, make_problem, coins, local_rounds, n_ro
     if n_rounds > local_rounds:
         tail_problem = make_problem(_gather_tail(local_problem.tables[:, 0], world, group))
         tail_buf = tail_problem.run_device(coins[local_rounds:])
-    rows = []
-    if red is not None:
-        rows += [_from_limbs(r) for r in red.cpu().tolist()]
-    n_local = len(rows)
-    if tail_buf is not None:
-        rows += samples_to_host(tail_buf, deg)
-    out = type(local_problem).complete_samples(rows[:n_local], coins[:n_local])
-    if tail_buf is not None:       # the first tail round is evaluated in full; later ones follow from their predecessor
-        out += type(local_problem).complete_samples(rows[n_local:], coins[n_local:])
+    on_device = (red is None or red.is_cuda) and (tail_buf is None or tail_buf.is_cuda)
+    if on_device:
+        # recombine the limb sums, fill g(1) of the later rounds and join the two parts on the device: one host copy
+        parts = []
+        if red is not None:
+            rows_dev = torch.zeros((local_rounds, 8), dtype=torch.int64, device=red.device)
+            rows_dev[:, :deg + 1] = _limbs_to_field_device(red).view(torch.int64)
+            rows_dev = rows_dev.view(torch.uint64)
+            _complete_on_device(rows_dev, deg, coins[:local_rounds])
+            parts.append(rows_dev)
+        if tail_buf is not None:      # the first tail round is evaluated in full; later ones follow from their predecessor
+            _complete_on_device(tail_buf, deg, coins[local_rounds:])
+            parts.append(tail_buf)
+        both = parts[0] if len(parts) == 1 else torch.cat([p.view(torch.int64) for p in parts]).view(torch.uint64)
+        out = samples_to_host(both, deg)
+    else:
+        rows = []
+        if red is not None:
+            rows += [_from_limbs(r) for r in red.cpu().tolist()]
+        n_local = len(rows)
+        if tail_buf is not None:
+            rows += samples_to_host(tail_buf, deg)
+        out = type(local_problem).complete_samples(rows[:n_local], coins[:n_local])
+        if tail_buf is not None:
+            out += type(local_problem).complete_samples(rows[n_local:], coins[n_local:])
     polys = [list(enumerate(ys)) for ys in out]
     claim = (out[0][0] + out[0][1]) % P
     return claim, polys, list(coins[:n_rounds])
