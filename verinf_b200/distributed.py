@@ -8,7 +8,7 @@ The reference is single-GPU; this is the sharding the path admits naturally:
   are all-gathered and every rank folds them into the leaves, then builds the Merkle tree;
 * sumcheck: rank g holds the entries i = g (mod G) of every table, so each fold stays local;
   per round the deg+1 partial sums are all-reduced (as 32-bit limbs, summed exactly, then
-  reduced mod p on the host); the last log2 G rounds run on the gathered G-entry tables.
+  reduced mod p); the last log2 G rounds run on the gathered G-entry tables.
 
 The collectives go through torch.distributed (NCCL on GPUs, gloo in the CPU tests); the
 local compute is injected (`backend`), so the host logic here is testable without a GPU.
