@@ -104,6 +104,12 @@ def test_argument_validation_without_gpu(lib):
     nfac[0] = 2
     assert L.vi_sumcheck_round(p, 16, 4, 12, 1, coefs, nfac, fac, 0, 0, p, p, None) != 0 and "power of two" in _err(lib)
     assert L.vi_sumcheck_round(p, 16, 9, 16, 1, coefs, nfac, fac, 0, 0, p, p, None) != 0
+    coins = (C.c_uint64 * 65)(*([3] * 65))
+    assert L.vi_sumcheck_complete(p, 65, 3, coins, None) != 0 and "64 rounds" in _err(lib)
+    assert L.vi_sumcheck_complete(p, 4, 8, coins, None) != 0 and "degree" in _err(lib)
+    assert L.vi_sumcheck_complete(p, 1, 3, coins, None) == 0                   # nothing to fill
+    coins[1] = (1 << 64) - 1
+    assert L.vi_sumcheck_complete(p, 4, 3, coins, None) != 0 and "canonical" in _err(lib)
 
 
 def test_shim_registers_reference_module_names(lib):
