@@ -57,6 +57,8 @@ def parse():
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / self-check leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--h2d-slices", type=int, default=32,
+                    help="slices of the end-to-end host-to-device copy (a slice is encoded and hashed when it lands)")
     ap.add_argument("--no-sharded", action="store_true", help="skip the sharded commit and sharded sumcheck blocks")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the 7B-layer commit+sumcheck and the fused K-quant encode on rank 0")
@@ -336,7 +338,7 @@ def run_native(a):
     # rank r's own batch = blocks 8r .. 8r+7 of the seeded stream; rank 0's batch is also the global
     # message of the sharded commit
     msg = gen_rows(torch, dev, 0, rows, k, rows, seed0=SEED + 8 * rank)
-    com = RowCommitter(rows, k, k, n, device=dev)
+    com = RowCommitter(rows, k, k, n, device=dev, h2d_slices=a.h2d_slices)
     roots = [torch.empty(32, dtype=torch.uint8, device=dev) for _ in range(world)] if world > 1 else None
 
     def step():

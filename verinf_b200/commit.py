@@ -73,7 +73,7 @@ class RowCommitter:
                       the root as 32 bytes on the host.
     """
 
-    def __init__(self, rows, ell, k_deg, n_lig, *, master_seed=None, device="cuda", h2d_slices=16):
+    def __init__(self, rows, ell, k_deg, n_lig, *, master_seed=None, device="cuda", h2d_slices=32):
         self.rows, self.ell, self.k, self.n = int(rows), int(ell), int(k_deg), int(n_lig)
         self.device = torch.device(device)
         self.seed = master_seed
