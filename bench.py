@@ -258,7 +258,10 @@ def cpu_self_check(a, torch, msg_dev, root_hex, k, n, payload):
 
 # ----------------------------------------------------------------------------- GPU arm
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clock and throttle-reason samples every 20 ms, started before the warm-up steps (the tool takes
+    a few hundred ms to deliver its first line); stop(t0, t1) keeps the samples stamped inside the timed region,
+    or, when the region was too short to hold two, those from the warm-up on (the GPU is under the same load)."""
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -271,11 +274,12 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -284,26 +288,29 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in open(self.path).read().splitlines():
             f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                rows.append((ts, float(f[2]), float(f[3]), [nm for nm, v in zip(names, f[6:10]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for nm, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(nm)
         try:
             os.unlink(self.path)
         except OSError:
             pass
-        if sm:
-            sm.sort()
-            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        window = "timed region"
+        inside = [r for r in rows if t0 is not None and t0 <= r[0] <= t1]
+        if len(inside) < 2:
+            inside, window = [r for r in rows if t1 is None or r[0] <= t1], "warm-up and timed region"
+        if inside:
+            sm = sorted(r[1] for r in inside)
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(r[2] for r in inside),
+                       reasons=sorted({x for r in inside for x in r[3]}), samples=len(inside), window=window)
         return out
 
 
@@ -352,24 +359,27 @@ def run_native(a):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(a.warmup, 3)):
-        step()
-    fence()
+    import datetime
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(a.warmup, 3)):
+        step()
+    fence()
     _lib.profile_enable(True)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     fence()
+    t_start = datetime.datetime.now()
     ev0.record()
     for _ in range(a.steps):
         root = step()
     ev1.record()
     fence()
+    t_end = datetime.datetime.now()
     ms = ev0.elapsed_time(ev1)
     prof = _lib.profile_read()
     _lib.profile_enable(False)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_start, t_end) if rank == 0 else None
     root_hex = bytes(root.cpu().tolist()).hex()
 
     # end to end: pinned host input -> H2D -> commit -> D2H root, all inside the timed region; beside it
