@@ -17,6 +17,7 @@ Jobs
   proofs:<module>  the same, for modules whose tests end in the Rust verifier: a stand-in records the
                    SHA-256 of every dumped proof file instead (see job_proofs)
   demo:<name>      demo/demo_<name>.py (llama7b): a whole transformer block proved and dumped; digest of the file
+  script:<name>    a reference test script that runs at import (difftest_lde_skip): the digests it prints
   kquant           kquant_cuda.kquant_to_field against gguf-py's dequantize -> quantize_to_field on seeded blocks
   commit_weights   core.commit_weights (prover/core.py:874-910) of a small seeded tape at the
                    production geometry: root and a digest of every Merkle level
@@ -155,6 +156,28 @@ def job_demo(name: str) -> dict:
     m = re.findall(r"prove:\s+([0-9.]+)s", log.getvalue())       # the demo's own timer around tape.prove
     return {"demo": name, "proof_sha256": h.hexdigest(), "proof_bytes": nbytes, "s": dt,
             "prove_s": float(m[-1]) if m else None, "peak_gb": torch.cuda.max_memory_allocated() / 1e9}
+
+
+def job_script(name: str) -> dict:
+    """A reference test script that runs at import (prover/tests/difftest_lde_skip.py: one tape at ELL = K = 8,
+    N = 32 proved with the codeword pass skipped where unread and forced, both proofs dumped and hashed):
+    executed as __main__ with its output captured; the SHA-256 values it prints are returned in order."""
+    import contextlib
+    import io
+    import re
+    import runpy
+    _fix_secrets()
+    sys.path.insert(0, str(REF / "prover" / "tests"))
+    log = io.StringIO()
+    code = None
+    with contextlib.redirect_stdout(log):
+        try:
+            runpy.run_path(str(REF / "prover" / "tests" / f"{name}.py"), run_name="__main__")
+        except SystemExit as e:         # the script ends in `raise SystemExit(0 if identical else 1)`
+            code = e.code
+    text = log.getvalue()
+    return {"script": name, "exit": code, "digests": re.findall(r"\b[0-9a-f]{64}\b", text),
+            "lines": len(text.splitlines())}
 
 
 def job_kquant() -> dict:
@@ -308,6 +331,8 @@ def main() -> None:
             out.update(job_proofs(a.job.split(":", 1)[1]))
         elif a.job.startswith("demo:"):
             out.update(job_demo(a.job.split(":", 1)[1]))
+        elif a.job.startswith("script:"):
+            out.update(job_script(a.job.split(":", 1)[1]))
         elif a.job == "kquant":
             out.update(job_kquant())
         elif a.job == "commit_weights":

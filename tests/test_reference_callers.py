@@ -173,3 +173,12 @@ def test_kquant_lift_equals_reference_kernel_and_gguf():
     for qt in ("Q4_K", "Q5_K", "Q6_K"):
         assert ours["kquant"][qt]["equals_gguf_numpy"] and ref["kquant"][qt]["equals_gguf_numpy"], qt
         assert ours["kquant"][qt]["sha256"] == ref["kquant"][qt]["sha256"], qt
+
+
+def test_lde_skip_difftest_smallest_geometry():
+    """prover/tests/difftest_lde_skip.py: a tape at ELL = K = 8, N = 32 (no pad slack, 8- and 32-point transforms)
+    proved under a pinned ZK seed with and without the codeword pass of the q-polynomial round; the script's
+    two proof digests must be equal to each other and to the ones the reference's kernels give."""
+    ours, ref = shim("script:difftest_lde_skip"), reference_or_skip("script:difftest_lde_skip")
+    assert ours["exit"] == 0 and len(ours["digests"]) == 2 and ours["digests"][0] == ours["digests"][1]
+    assert ours["digests"] == ref["digests"]
